@@ -1,0 +1,117 @@
+/*
+ * ternel_b200 — C ABI of the B200-native packed ternary (TQ1_G128) linear and
+ * embedding path. Plain pointers and sizes only; no C++ or torch types.
+ *
+ * Weight layout ("canonical blocks"): W[N out][K in], K % 128 == 0, stored
+ * row-major as 28-byte blocks [N][K/128][28]:
+ *   byte 0..1  raw little-endian FP16 scale bits
+ *   byte 2+j   sum_{i<5} c[5j+i]*3^i  (j = 0..24, value <= 242)
+ *   byte 27    c[125] + 3 c[126] + 9 c[127]       (value <= 26)
+ * c in {0,1,2}; logical weight = (c - 1) * scale.
+ *
+ * Each entry point cites the interface of the reference project
+ * (inductiveML/ternel, paths relative to its root) that it stands in for.
+ *
+ * Conventions: every function returns TQ1_OK (0) or a negative TQ1_ERR_* code
+ * and never throws, aborts or allocates device memory. Device entry points are
+ * stream-ordered and asynchronous: they enqueue work on `stream` (a
+ * cudaStream_t passed as void*; NULL = the legacy default stream) and return
+ * without synchronising. tq1_last_error() gives a per-thread message for the
+ * last failing call.
+ */
+#ifndef TERNEL_B200_H
+#define TERNEL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TQ1_OK 0
+#define TQ1_ERR_INVALID (-1)   /* bad argument, shape, alignment or null pointer */
+#define TQ1_ERR_FORMAT (-2)    /* non-ternary code or illegal base-3 byte (fail closed) */
+#define TQ1_ERR_CUDA (-3)      /* a CUDA runtime call or kernel launch failed */
+#define TQ1_ERR_WORKSPACE (-4) /* workspace missing, misaligned or too small */
+
+#define TQ1_GROUP 128
+#define TQ1_BLOCK_BYTES 28
+
+/* Library ABI version (bumped when a signature changes). */
+int tq1_abi_version(void);
+
+/* Message for the last failing call on this thread ("" if none). */
+const char *tq1_last_error(void);
+
+/* ---- host-side format codec -------------------------------------------- */
+
+/* Replaces encode_tq1_blocks (src/bonsai_tq1/format.py:66-91).
+ * scales: [groups][2] raw FP16 bytes; trits: [groups][128] in {0,1,2};
+ * blocks: [groups][28] out. Any trit > 2 => TQ1_ERR_FORMAT, *n_bad = count,
+ * nothing written. */
+int tq1_pack_blocks(const uint8_t *scales, const uint8_t *trits, uint8_t *blocks,
+                    int64_t groups, int64_t *n_bad);
+
+/* Replaces decode_tq1_blocks (src/bonsai_tq1/format.py:94-122). With
+ * validate != 0 any byte > 242 in slots 0..24 or > 26 in the tail slot gives
+ * TQ1_ERR_FORMAT with the two counts, nothing written. */
+int tq1_unpack_blocks(const uint8_t *blocks, uint8_t *scales, uint8_t *trits,
+                      int64_t groups, int validate, int64_t *n_bad_full, int64_t *n_bad_tail);
+
+/* The load-time scan of validate_packed_codes (src/ternel_mlx/packing.py:29-48)
+ * and ggml_validate_row_data's TQ1 case (patches/prism-tq1-g128-distribution.patch:449-468),
+ * over canonical blocks in host memory. */
+int tq1_validate_blocks(const uint8_t *blocks, int64_t groups,
+                        int64_t *n_bad_full, int64_t *n_bad_tail);
+
+/* Canonical [rows][groups][28] <-> the reference's code-position-major tiles
+ * codes u8[tiles][groups][26][tile], scales u16[tiles][groups][tile]
+ * (reorder_tensor_arrays / restore_tensor_arrays, src/bonsai_tq1/lut23_reorder.py:126-165;
+ * pack_blocks / unpack_blocks, src/ternel_mlx/packing.py:51-82). Host memory.
+ * rows % tile must be 0 (the MLX layout never pads: src/ternel_mlx/layout.py:76-80). */
+int tq1_tile_blocks(const uint8_t *blocks, uint8_t *codes, uint16_t *scales,
+                    int64_t rows, int64_t groups_per_row, int64_t tile);
+int tq1_untile_blocks(const uint8_t *codes, const uint16_t *scales, uint8_t *blocks,
+                      int64_t rows, int64_t groups_per_row, int64_t tile);
+
+/* ---- device entry points ------------------------------------------------ */
+
+/* Same scan as tq1_validate_blocks over blocks in device memory; counts_dev is
+ * a device int64[2] {n_bad_full, n_bad_tail} that the call zeroes first. */
+int tq1_validate_blocks_device(const uint8_t *blocks_dev, int64_t groups,
+                               int64_t *counts_dev, void *stream);
+
+/* Scratch the linear entry point needs for this shape (0 when none). The
+ * caller owns the buffer, as the caller of launch_tq1_lut23_smem_streamk owns
+ * its workspace (cuda/tq1_lut23_streamk.cu:320-367, lut23_workspace_bytes). */
+size_t tq1_linear_workspace_bytes(int M, int N, int K);
+
+/* y[m][n] = sum_g f32(scale[n][g]) * sum_{k in g} (c[n][k]-1) * f32(x[m][k]),
+ * FP32 accumulation, one narrowing at the store.
+ * Replaces tq1_matmul / tq1_gemm behind packed_matmul
+ * (src/ternel_mlx/kernels.py:1215-1271,1287-1357; src/ternel_mlx/modules.py:425-457)
+ * and launch_tq1_g128_gemv_v1 / launch_tq1_lut23_smem_streamk
+ * (cuda/tq1_g128_gemv.cu:144-193, cuda/tq1_lut23_streamk.cu:320-367).
+ *   blocks    device, canonical [N][K/128][28], 4-byte aligned
+ *   x         device FP16 [M][K] row-major, 16-byte aligned
+ *   y         device [M][N] row-major, FP16 (y_is_f32 == 0) or FP32
+ *   workspace device, >= tq1_linear_workspace_bytes(M,N,K) bytes, 256-byte
+ *             aligned (may be NULL when that is 0)
+ * The kernel is chosen from M: 1 => streaming GEMV, 2..16 => small-batch
+ * split-K GEMV, larger => tiled GEMM. Illegal code bytes must have been
+ * rejected at load (tq1_validate_blocks*): the kernels carry no clamp. */
+int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
+                   int M, int N, int K, void *workspace, size_t workspace_bytes, void *stream);
+
+/* out[t][k] = (c[id_t][k]-1) * scale[id_t][k/128], exact; an id outside [0,V)
+ * gives a zero row. Replaces tq1_get_rows (src/ternel_mlx/kernels.py:1360-1398,
+ * 863-901) and k_get_rows_tq1_g128 (patches/prism-tq1-g128-distribution.patch:132-171).
+ *   ids  device int64[T];  out device [T][K], FP16 or FP32 (out_is_f32) */
+int tq1_embedding_f16(const uint8_t *blocks, const int64_t *ids, void *out, int out_is_f32,
+                      int64_t T, int64_t V, int K, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TERNEL_B200_H */

@@ -1,0 +1,65 @@
+"""ctypes binding of the C ABI declared in include/ternel_b200.h.
+
+There is no fallback: if the shared library is missing the import of any
+compute entry point raises, so a run can never silently continue on a CPU or
+PyTorch path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p, POINTER
+
+from .build import LIB_PATH
+
+TQ1_OK = 0
+TQ1_ERR_INVALID = -1
+TQ1_ERR_FORMAT = -2
+TQ1_ERR_CUDA = -3
+TQ1_ERR_WORKSPACE = -4
+
+# name -> (restype, argtypes); must list every symbol the header declares.
+SIGNATURES = {
+    "tq1_abi_version": (c_int, []),
+    "tq1_last_error": (c_char_p, []),
+    "tq1_pack_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, POINTER(c_int64)]),
+    "tq1_unpack_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                                  POINTER(c_int64), POINTER(c_int64)]),
+    "tq1_validate_blocks": (c_int, [c_void_p, c_int64, POINTER(c_int64), POINTER(c_int64)]),
+    "tq1_tile_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
+    "tq1_untile_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
+    "tq1_validate_blocks_device": (c_int, [c_void_p, c_int64, c_void_p, c_void_p]),
+    "tq1_linear_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "tq1_linear_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                               c_void_p, c_size_t, c_void_p]),
+    "tq1_embedding_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int,
+                                  c_void_p]),
+}
+
+_lib: ctypes.CDLL | None = None
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises loudly if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise NativeLibraryMissing(
+                f"{LIB_PATH} is missing: build it with `python -m ternel_b200.build` "
+                "(there is no CPU or PyTorch fallback for the packed ternary kernels)"
+            )
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def last_error() -> str:
+    return (lib().tq1_last_error() or b"").decode("utf-8", "replace")

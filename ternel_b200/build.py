@@ -1,0 +1,60 @@
+"""Compile the CUDA sources into the in-tree C-ABI shared library (sm_100a only)."""
+
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+from pathlib import Path
+
+PACKAGE_DIR = Path(__file__).resolve().parent
+CSRC_DIR = PACKAGE_DIR / "csrc"
+LIB_DIR = PACKAGE_DIR / "_lib"
+LIB_PATH = LIB_DIR / "libternel_b200.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-shared",
+]
+
+
+def sources() -> list[Path]:
+    return sorted(CSRC_DIR.glob("*.cu"))
+
+
+def _nvcc() -> str:
+    found = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(found).exists():
+        raise RuntimeError("nvcc not found; the library can only be built with the CUDA toolkit")
+    return found
+
+
+def is_stale() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    built = LIB_PATH.stat().st_mtime
+    deps = sources() + list(CSRC_DIR.glob("*.cuh")) + [PACKAGE_DIR.parent / "include" / "ternel_b200.h"]
+    return any(p.stat().st_mtime > built for p in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Build ``_lib/libternel_b200.so`` when missing or older than a source file."""
+    if not force and not is_stale():
+        return LIB_PATH
+    LIB_DIR.mkdir(exist_ok=True)
+    tmp = LIB_DIR / f".libternel_b200.{os.getpid()}.so"
+    cmd = [_nvcc(), *NVCC_FLAGS, *( ["-Xptxas", "-v"] if verbose else [] ),
+           "-o", str(tmp), *map(str, sources())]
+    done = subprocess.run(cmd, capture_output=True, text=True)
+    if done.returncode != 0:
+        tmp.unlink(missing_ok=True)
+        raise RuntimeError(f"nvcc failed:\n{done.stdout}\n{done.stderr}")
+    if verbose:
+        print(done.stderr)
+    os.replace(tmp, LIB_PATH)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build(force=True, verbose=True))

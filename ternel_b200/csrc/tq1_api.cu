@@ -1,0 +1,50 @@
+// C-ABI entry points of the linear and embedding path: argument checks and
+// kernel selection. Checks mirror the reference wrappers' (_check_packed /
+// _check_activations, src/ternel_mlx/kernels.py:1191-1212,1274-1284): shape and
+// dtype violations are reported before anything is launched.
+#include "tq1_common.cuh"
+
+using namespace tq1;
+
+extern "C" {
+
+size_t tq1_linear_workspace_bytes(int M, int N, int K) {
+    (void)M; (void)N; (void)K;
+    return 0;
+}
+
+int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
+                   int M, int N, int K, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!blocks || !x || !y) return fail(TQ1_ERR_INVALID, "tq1_linear_f16: null pointer");
+    if (M <= 0) return fail(TQ1_ERR_INVALID, "activations have an empty batch dimension");
+    if (N <= 0 || K <= 0)
+        return fail(TQ1_ERR_INVALID, "tensor dimensions must be positive, got %dx%d", N, K);
+    if (K % kGroup)
+        return fail(TQ1_ERR_INVALID, "%d columns is not a multiple of the 128-weight group", K);
+    if (reinterpret_cast<uintptr_t>(blocks) & 3)
+        return fail(TQ1_ERR_INVALID, "tq1_linear_f16: blocks must be 4-byte aligned");
+    if (reinterpret_cast<uintptr_t>(x) & 15)
+        return fail(TQ1_ERR_INVALID, "tq1_linear_f16: x must be 16-byte aligned");
+    const size_t need = tq1_linear_workspace_bytes(M, N, K);
+    if (need && (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)))
+        return fail(TQ1_ERR_WORKSPACE, "tq1_linear_f16: workspace of %zu bytes (256-byte aligned) required", need);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return launch_gemv_rows(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, s);
+}
+
+int tq1_embedding_f16(const uint8_t *blocks, const int64_t *ids, void *out, int out_is_f32,
+                      int64_t T, int64_t V, int K, void *stream) {
+    if (!blocks || !ids || !out) return fail(TQ1_ERR_INVALID, "tq1_embedding_f16: null pointer");
+    if (T <= 0) return fail(TQ1_ERR_INVALID, "indices are empty");
+    if (V <= 0 || K <= 0)
+        return fail(TQ1_ERR_INVALID, "tensor dimensions must be positive, got %lldx%d", (long long)V, K);
+    if (K % kGroup)
+        return fail(TQ1_ERR_INVALID, "%d columns is not a multiple of the 128-weight group", K);
+    if (reinterpret_cast<uintptr_t>(blocks) & 3)
+        return fail(TQ1_ERR_INVALID, "tq1_embedding_f16: blocks must be 4-byte aligned");
+    if (reinterpret_cast<uintptr_t>(out) & 15)
+        return fail(TQ1_ERR_INVALID, "tq1_embedding_f16: out must be 16-byte aligned");
+    return launch_embedding(blocks, ids, out, out_is_f32 != 0, T, V, K, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,204 @@
+// Host-side TQ1_G128 codec and the device-side load-time byte scan.
+//
+// pack/unpack/validate restate src/bonsai_tq1/format.py:66-122 of the reference;
+// tile/untile restate src/bonsai_tq1/lut23_reorder.py:126-165 for row counts the
+// tile divides (the MLX layout, src/ternel_mlx/layout.py:76-80).
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "tq1_common.cuh"
+
+namespace tq1 {
+
+static thread_local char g_error[512] = "";
+
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t err, const char *what) {
+    return fail(TQ1_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
+}
+
+static void scan_host(const uint8_t *blocks, int64_t groups, int64_t *bad_full, int64_t *bad_tail) {
+    int64_t bf = 0, bt = 0;
+    for (int64_t g = 0; g < groups; ++g) {
+        const uint8_t *b = blocks + g * kBlockBytes;
+        for (int j = 2; j < 27; ++j) bf += b[j] > kMaxFull;
+        bt += b[27] > kMaxTail;
+    }
+    *bad_full = bf;
+    *bad_tail = bt;
+}
+
+// One thread per block; per-CTA counts are combined with one atomic each.
+__global__ void __launch_bounds__(256) validate_kernel(const uint32_t *__restrict__ words,
+                                                       int64_t groups,
+                                                       unsigned long long *__restrict__ counts) {
+    unsigned bf = 0, bt = 0;
+    for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < groups;
+         g += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t *w = words + g * kBlockWords;
+        uint32_t w0 = w[0];
+        bf += ((w0 >> 16) & 0xffu) > kMaxFull;
+        bf += (w0 >> 24) > kMaxFull;
+#pragma unroll
+        for (int i = 1; i < 7; ++i) {
+            uint32_t v = w[i];
+            bf += (v & 0xffu) > kMaxFull;
+            bf += ((v >> 8) & 0xffu) > kMaxFull;
+            bf += ((v >> 16) & 0xffu) > kMaxFull;
+            if (i < 6) bf += (v >> 24) > kMaxFull;
+            else bt += (v >> 24) > kMaxTail;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        bf += __shfl_xor_sync(0xffffffffu, bf, o);
+        bt += __shfl_xor_sync(0xffffffffu, bt, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        if (bf) atomicAdd(&counts[0], (unsigned long long)bf);
+        if (bt) atomicAdd(&counts[1], (unsigned long long)bt);
+    }
+}
+
+int launch_validate(const uint8_t *blocks, int64_t groups, int64_t *counts, cudaStream_t stream) {
+    cudaError_t err = cudaMemsetAsync(counts, 0, 2 * sizeof(int64_t), stream);
+    if (err != cudaSuccess) return cuda_fail(err, "tq1_validate_blocks_device: memset");
+    if (groups == 0) return TQ1_OK;
+    int64_t ctas = (groups + 255) / 256;
+    if (ctas > 148 * 8) ctas = 148 * 8;
+    validate_kernel<<<(unsigned)ctas, 256, 0, stream>>>(
+        reinterpret_cast<const uint32_t *>(blocks), groups,
+        reinterpret_cast<unsigned long long *>(counts));
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return cuda_fail(err, "tq1_validate_blocks_device: launch");
+    return TQ1_OK;
+}
+
+}  // namespace tq1
+
+using namespace tq1;
+
+extern "C" {
+
+int tq1_abi_version(void) { return 1; }
+
+const char *tq1_last_error(void) { return g_error; }
+
+int tq1_pack_blocks(const uint8_t *scales, const uint8_t *trits, uint8_t *blocks,
+                    int64_t groups, int64_t *n_bad) {
+    if (groups < 0 || (groups > 0 && (!scales || !trits || !blocks)))
+        return fail(TQ1_ERR_INVALID, "tq1_pack_blocks: null pointer or negative group count");
+    int64_t bad = 0;
+    for (int64_t i = 0; i < groups * kGroup; ++i) bad += trits[i] > 2;
+    if (n_bad) *n_bad = bad;
+    if (bad) return fail(TQ1_ERR_FORMAT, "source contains %lld non-ternary code(s)", (long long)bad);
+    for (int64_t g = 0; g < groups; ++g) {
+        const uint8_t *c = trits + g * kGroup;
+        uint8_t *b = blocks + g * kBlockBytes;
+        b[0] = scales[2 * g];
+        b[1] = scales[2 * g + 1];
+        for (int j = 0; j < kFullBytes; ++j) {
+            unsigned v = 0;
+            for (int i = 4; i >= 0; --i) v = v * 3 + c[5 * j + i];
+            b[2 + j] = (uint8_t)v;
+        }
+        b[27] = (uint8_t)(c[125] + 3u * c[126] + 9u * c[127]);
+    }
+    return TQ1_OK;
+}
+
+int tq1_validate_blocks(const uint8_t *blocks, int64_t groups,
+                        int64_t *n_bad_full, int64_t *n_bad_tail) {
+    if (groups < 0 || (groups > 0 && !blocks))
+        return fail(TQ1_ERR_INVALID, "tq1_validate_blocks: null pointer or negative group count");
+    int64_t bf = 0, bt = 0;
+    scan_host(blocks, groups, &bf, &bt);
+    if (n_bad_full) *n_bad_full = bf;
+    if (n_bad_tail) *n_bad_tail = bt;
+    if (bf || bt)
+        return fail(TQ1_ERR_FORMAT, "invalid base-3 bytes: regular=%lld, tail=%lld",
+                    (long long)bf, (long long)bt);
+    return TQ1_OK;
+}
+
+int tq1_unpack_blocks(const uint8_t *blocks, uint8_t *scales, uint8_t *trits,
+                      int64_t groups, int validate, int64_t *n_bad_full, int64_t *n_bad_tail) {
+    if (groups < 0 || (groups > 0 && (!blocks || !scales || !trits)))
+        return fail(TQ1_ERR_INVALID, "tq1_unpack_blocks: null pointer or negative group count");
+    if (n_bad_full) *n_bad_full = 0;
+    if (n_bad_tail) *n_bad_tail = 0;
+    if (validate) {
+        int rc = tq1_validate_blocks(blocks, groups, n_bad_full, n_bad_tail);
+        if (rc != TQ1_OK) return rc;
+    }
+    uint8_t table[256][5];
+    for (unsigned v = 0; v < 256; ++v) {
+        unsigned r = v;
+        for (int i = 0; i < 5; ++i) { table[v][i] = (uint8_t)(r % 3); r /= 3; }
+    }
+    for (int64_t g = 0; g < groups; ++g) {
+        const uint8_t *b = blocks + g * kBlockBytes;
+        uint8_t *c = trits + g * kGroup;
+        scales[2 * g] = b[0];
+        scales[2 * g + 1] = b[1];
+        for (int j = 0; j < kFullBytes; ++j) memcpy(c + 5 * j, table[b[2 + j]], 5);
+        memcpy(c + 125, table[b[27]], 3);
+    }
+    return TQ1_OK;
+}
+
+int tq1_tile_blocks(const uint8_t *blocks, uint8_t *codes, uint16_t *scales,
+                    int64_t rows, int64_t gpr, int64_t tile) {
+    if (rows <= 0 || gpr <= 0 || tile <= 0 || !blocks || !codes || !scales)
+        return fail(TQ1_ERR_INVALID, "tq1_tile_blocks: dimensions must be positive and pointers non-null");
+    if (rows % tile)
+        return fail(TQ1_ERR_INVALID, "tile %lld does not divide %lld rows", (long long)tile, (long long)rows);
+    for (int64_t r = 0; r < rows; ++r) {
+        int64_t t = r / tile, in = r % tile;
+        for (int64_t g = 0; g < gpr; ++g) {
+            const uint8_t *b = blocks + (r * gpr + g) * kBlockBytes;
+            scales[(t * gpr + g) * tile + in] = (uint16_t)(b[0] | (b[1] << 8));
+            uint8_t *dst = codes + ((t * gpr + g) * kCodeBytes) * tile + in;
+            for (int s = 0; s < kCodeBytes; ++s) dst[s * tile] = b[2 + s];
+        }
+    }
+    return TQ1_OK;
+}
+
+int tq1_untile_blocks(const uint8_t *codes, const uint16_t *scales, uint8_t *blocks,
+                      int64_t rows, int64_t gpr, int64_t tile) {
+    if (rows <= 0 || gpr <= 0 || tile <= 0 || !blocks || !codes || !scales)
+        return fail(TQ1_ERR_INVALID, "tq1_untile_blocks: dimensions must be positive and pointers non-null");
+    if (rows % tile)
+        return fail(TQ1_ERR_INVALID, "tile %lld does not divide %lld rows", (long long)tile, (long long)rows);
+    for (int64_t r = 0; r < rows; ++r) {
+        int64_t t = r / tile, in = r % tile;
+        for (int64_t g = 0; g < gpr; ++g) {
+            uint8_t *b = blocks + (r * gpr + g) * kBlockBytes;
+            uint16_t s = scales[(t * gpr + g) * tile + in];
+            b[0] = (uint8_t)(s & 0xff);
+            b[1] = (uint8_t)(s >> 8);
+            const uint8_t *src = codes + ((t * gpr + g) * kCodeBytes) * tile + in;
+            for (int k = 0; k < kCodeBytes; ++k) b[2 + k] = src[k * tile];
+        }
+    }
+    return TQ1_OK;
+}
+
+int tq1_validate_blocks_device(const uint8_t *blocks_dev, int64_t groups,
+                               int64_t *counts_dev, void *stream) {
+    if (groups < 0 || !counts_dev || (groups > 0 && !blocks_dev))
+        return fail(TQ1_ERR_INVALID, "tq1_validate_blocks_device: null pointer or negative group count");
+    if (reinterpret_cast<uintptr_t>(blocks_dev) & 3)
+        return fail(TQ1_ERR_INVALID, "tq1_validate_blocks_device: blocks must be 4-byte aligned");
+    return launch_validate(blocks_dev, groups, counts_dev, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

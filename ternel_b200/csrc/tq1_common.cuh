@@ -1,0 +1,40 @@
+// Shared constants and helpers for the TQ1_G128 kernels (sm_100a).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ternel_b200.h"
+
+namespace tq1 {
+
+constexpr int kGroup = TQ1_GROUP;             // weights per block
+constexpr int kBlockBytes = TQ1_BLOCK_BYTES;  // bytes per block
+constexpr int kBlockWords = kBlockBytes / 4;  // 7 x 32-bit words, always 4-byte aligned
+constexpr int kCodeBytes = 26;
+constexpr int kFullBytes = 25;
+constexpr int kMaxFull = 242;
+constexpr int kMaxTail = 26;
+
+// Records a message for tq1_last_error() and returns `code`.
+int fail(int code, const char *fmt, ...);
+int cuda_fail(cudaError_t err, const char *what);
+
+// Launchers implemented one per .cu file; all enqueue on `stream` and return a status.
+int launch_validate(const uint8_t *blocks, int64_t groups, int64_t *counts, cudaStream_t stream);
+int launch_embedding(const uint8_t *blocks, const int64_t *ids, void *out, bool out_f32,
+                     int64_t T, int64_t V, int K, cudaStream_t stream);
+int launch_gemv_rows(const uint8_t *blocks, const __half *x, void *y, bool y_f32,
+                     int M, int N, int K, cudaStream_t stream);
+
+// Five base-3 digits of a byte packed two bits each (digit i at bits 2i..2i+1).
+__host__ __device__ inline uint32_t trits_2bit(uint32_t byte) {
+    uint32_t e = 0;
+    for (int i = 0; i < 5; ++i) {
+        e |= (byte % 3u) << (2 * i);
+        byte /= 3u;
+    }
+    return e;
+}
+
+}  // namespace tq1

@@ -1,0 +1,157 @@
+"""Layout descriptor and the bridge to the reference's tiled arrays.
+
+``PackedTensorLayout`` keeps the reference's shape and byte accounting
+(src/ternel_mlx/layout.py:41-147); ``pack_blocks`` / ``unpack_blocks`` /
+``validate_packed_codes`` keep the contract of src/ternel_mlx/packing.py:29-82.
+On the device this library stores the *canonical* row-major blocks; the tiled
+``codes``/``scales`` pair is only an interchange form accepted at load time.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _native
+from .format import BLOCK_BYTES, BLOCK_SIZE, MAX_FULL_CODE_BYTE, MAX_TAIL_CODE_BYTE, FormatError, check
+
+PREFERRED_TILE = 256
+CODE_SLOTS = 26
+FULL_CODE_SLOTS = 25
+SCALE_BYTES = BLOCK_BYTES - CODE_SLOTS
+SCALE_VIEW_DTYPE = np.dtype("<u2")
+CODES_SUFFIX = "codes"
+SCALES_SUFFIX = "scales"
+
+
+def select_tile(rows: int) -> int:
+    """256 when it divides ``rows``, otherwise ``rows`` itself (no padded rows)."""
+    if rows <= 0:
+        raise FormatError(f"row count must be positive, got {rows}")
+    return PREFERRED_TILE if rows % PREFERRED_TILE == 0 else rows
+
+
+@dataclass(frozen=True)
+class PackedTensorLayout:
+    """Shape and byte accounting for one packed tensor: ``rows`` = output N, ``columns`` = K."""
+
+    rows: int
+    columns: int
+    tile: int
+
+    def __post_init__(self) -> None:
+        if self.rows <= 0 or self.columns <= 0:
+            raise FormatError(f"tensor dimensions must be positive, got {self.rows}x{self.columns}")
+        if self.columns % BLOCK_SIZE:
+            raise FormatError(
+                f"{self.columns} columns is not a multiple of the {BLOCK_SIZE}-weight group")
+        if self.tile <= 0:
+            raise FormatError(f"tile must be positive, got {self.tile}")
+        if self.rows % self.tile:
+            raise FormatError(
+                f"tile {self.tile} does not divide {self.rows} rows; the layout does not pad rows")
+
+    @classmethod
+    def for_tensor(cls, rows: int, columns: int) -> "PackedTensorLayout":
+        return cls(rows=rows, columns=columns, tile=select_tile(rows))
+
+    @property
+    def groups_per_row(self) -> int:
+        return self.columns // BLOCK_SIZE
+
+    @property
+    def tiles(self) -> int:
+        return self.rows // self.tile
+
+    @property
+    def groups(self) -> int:
+        return self.rows * self.groups_per_row
+
+    @property
+    def codes_shape(self) -> tuple[int, int, int, int]:
+        return (self.tiles, self.groups_per_row, CODE_SLOTS, self.tile)
+
+    @property
+    def scales_shape(self) -> tuple[int, int, int]:
+        return (self.tiles, self.groups_per_row, self.tile)
+
+    @property
+    def blocks_shape(self) -> tuple[int, int, int]:
+        """Canonical device layout: ``[row][group][28]``."""
+        return (self.rows, self.groups_per_row, BLOCK_BYTES)
+
+    @property
+    def codes_bytes(self) -> int:
+        return self.groups * CODE_SLOTS
+
+    @property
+    def scales_bytes(self) -> int:
+        return self.groups * SCALE_BYTES
+
+    @property
+    def payload_bytes(self) -> int:
+        return self.codes_bytes + self.scales_bytes
+
+    @property
+    def canonical_bytes(self) -> int:
+        return self.groups * BLOCK_BYTES
+
+    @property
+    def bits_per_weight(self) -> float:
+        return self.payload_bytes * 8 / (self.rows * self.columns)
+
+
+def validate_packed_codes(codes: np.ndarray) -> None:
+    """Reject any tiled code byte above 242 (full slots) or 26 (tail slot)."""
+    array = np.asarray(codes)
+    if array.dtype != np.uint8:
+        raise FormatError(f"codes must be uint8, got {array.dtype}")
+    if array.ndim != 4:
+        raise FormatError(f"codes must be 4-D (tiles, groups, slots, tile), got {array.shape}")
+    invalid_full = int(np.count_nonzero(array[:, :, :FULL_CODE_SLOTS, :] > MAX_FULL_CODE_BYTE))
+    invalid_tail = int(np.count_nonzero(array[:, :, FULL_CODE_SLOTS, :] > MAX_TAIL_CODE_BYTE))
+    if invalid_full or invalid_tail:
+        raise FormatError(
+            f"packed codes contain out-of-range base-3 bytes: regular={invalid_full} "
+            f"(max {MAX_FULL_CODE_BYTE}), tail={invalid_tail} (max {MAX_TAIL_CODE_BYTE})")
+
+
+def _ptr(array: np.ndarray) -> ctypes.c_void_p:
+    return ctypes.c_void_p(array.ctypes.data)
+
+
+def pack_blocks(blocks: np.ndarray, *, layout: PackedTensorLayout) -> tuple[np.ndarray, np.ndarray]:
+    """Canonical ``(rows, groups, 28)`` -> tiled ``(codes uint8, scales uint16)``."""
+    source = np.asarray(blocks)
+    if source.dtype != np.uint8:
+        raise FormatError(f"canonical blocks must be uint8, got {source.dtype}")
+    if source.shape != layout.blocks_shape:
+        raise FormatError(f"expected canonical blocks of shape {layout.blocks_shape}, got {source.shape}")
+    source = np.ascontiguousarray(source)
+    codes = np.empty(layout.codes_shape, dtype=np.uint8)
+    scales = np.empty(layout.scales_shape, dtype=SCALE_VIEW_DTYPE)
+    check(_native.lib().tq1_tile_blocks(_ptr(source), _ptr(codes), _ptr(scales), layout.rows,
+                                        layout.groups_per_row, layout.tile))
+    return codes, scales
+
+
+def unpack_blocks(codes: np.ndarray, scales: np.ndarray, *, layout: PackedTensorLayout) -> np.ndarray:
+    """Inverse of :func:`pack_blocks`."""
+    code_array = np.asarray(codes)
+    scale_array = np.asarray(scales)
+    if code_array.dtype != np.uint8:
+        raise FormatError(f"codes must be uint8, got {code_array.dtype}")
+    if scale_array.dtype != SCALE_VIEW_DTYPE:
+        raise FormatError(f"scales must be little-endian uint16, got {scale_array.dtype}")
+    if code_array.shape != layout.codes_shape:
+        raise FormatError(f"codes shape {code_array.shape} does not match {layout.codes_shape}")
+    if scale_array.shape != layout.scales_shape:
+        raise FormatError(f"scales shape {scale_array.shape} does not match {layout.scales_shape}")
+    code_array = np.ascontiguousarray(code_array)
+    scale_array = np.ascontiguousarray(scale_array)
+    blocks = np.empty(layout.blocks_shape, dtype=np.uint8)
+    check(_native.lib().tq1_untile_blocks(_ptr(code_array), _ptr(scale_array), _ptr(blocks),
+                                          layout.rows, layout.groups_per_row, layout.tile))
+    return blocks
