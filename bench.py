@@ -210,8 +210,8 @@ def run_gpu_arm(args) -> None:
         from oracle import c_oracle, tq1_oracle as o
         stack.step()
         torch.cuda.synchronize()
-        name, n, k = stack.projections[1]
-        blocks = stack.weights[-1][1].cpu().numpy()
+        name, n, k = stack.projections[-1]     # the last writer of its output buffer
+        blocks = stack.weights[-1][-1].cpu().numpy()
         x = stack.inputs[k].float().cpu().numpy()
         want = c_oracle.matmul_f32(blocks, x, rows=n // world, columns=k)
         got = (stack.outputs[n][0] if world > 1 else stack.outputs[n]).float().cpu().numpy().reshape(args.batch, -1)

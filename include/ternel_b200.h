@@ -97,7 +97,10 @@ size_t tq1_linear_workspace_bytes(int M, int N, int K);
  *   x         device FP16 [M][K] row-major, 16-byte aligned
  *   y         device [M][N] row-major, FP16 (y_is_f32 == 0) or FP32
  *   workspace device, >= tq1_linear_workspace_bytes(M,N,K) bytes, 256-byte
- *             aligned (may be NULL when that is 0)
+ *             aligned (may be NULL when that is 0). It must be zero-filled
+ *             once before its first use; every call leaves it ready for the
+ *             next one, of any shape. Calls that may overlap on the GPU
+ *             (different streams) need separate workspaces.
  * The kernel is chosen from M: 1 => streaming GEMV, 2..16 => small-batch
  * split-K GEMV, larger => tiled GEMM. Illegal code bytes must have been
  * rejected at load (tq1_validate_blocks*): the kernels carry no clamp. */

@@ -9,7 +9,8 @@ using namespace tq1;
 extern "C" {
 
 size_t tq1_linear_workspace_bytes(int M, int N, int K) {
-    (void)M; (void)N; (void)K;
+    if (M <= 0 || N <= 0 || K <= 0 || K % kGroup) return 0;
+    if (M == 1 && gemv_stream_shape_ok(N, K)) return gemv_stream_workspace_bytes(N, K);
     return 0;
 }
 
@@ -29,6 +30,8 @@ int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
     if (need && (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)))
         return fail(TQ1_ERR_WORKSPACE, "tq1_linear_f16: workspace of %zu bytes (256-byte aligned) required", need);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (M == 1 && gemv_stream_supported(blocks, N, K))
+        return launch_gemv_stream(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, N, K, workspace, s);
     return launch_gemv_rows(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, s);
 }
 

@@ -27,6 +27,13 @@ int launch_embedding(const uint8_t *blocks, const int64_t *ids, void *out, bool 
 int launch_gemv_rows(const uint8_t *blocks, const __half *x, void *y, bool y_f32,
                      int M, int N, int K, cudaStream_t stream);
 
+// Streaming batch-1 GEMV (TMA + integer tensor cores); needs K % 512 == 0 and 16-byte aligned blocks.
+bool gemv_stream_shape_ok(int N, int K);
+bool gemv_stream_supported(const uint8_t *blocks, int N, int K);
+size_t gemv_stream_workspace_bytes(int N, int K);
+int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K,
+                       void *workspace, cudaStream_t stream);
+
 // Five base-3 digits of a byte packed two bits each (digit i at bits 2i..2i+1).
 __host__ __device__ inline uint32_t trits_2bit(uint32_t byte) {
     uint32_t e = 0;
