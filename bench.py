@@ -44,6 +44,8 @@ def parse_args():
     p.add_argument("--layers", type=int, default=64)
     p.add_argument("--batch", type=int, default=1)
     p.add_argument("--no-graph", action="store_true", help="launch every kernel from the host each step")
+    p.add_argument("--unfused", action="store_true",
+                   help="seven launches per layer (q,k,v,o,gate,up,down) instead of four (qkv,o,gate_up,down)")
     p.add_argument("--skip-cpu-baseline", action="store_true")
     p.add_argument("--skip-e2e", action="store_true")
     return p.parse_args()
@@ -56,6 +58,8 @@ def workload_config(args) -> dict:
         "batch": args.batch,
         "shapes_NxK": ["5120x5120 (q,o)", "1024x5120 (k,v)", "17408x5120 (gate,up)", "5120x17408 (down)"],
         "embedding": "151936x5120 packed, one row per sequence",
+        "launches_per_layer": "7 (q,k,v,o,gate,up,down)" if args.unfused else
+                              "4 (q|k|v and gate|up stored row-concatenated: 7168x5120, 5120x5120, 34816x5120, 5120x17408)",
         "packed_weight_bytes": None,   # filled in
         "parallelism": f"row-sharded x{args.gpus}" if args.gpus > 1 else "single GPU",
         "l2_policy": "inputs larger than L2 (each step streams every layer's distinct weights)",
@@ -204,7 +208,7 @@ def run_gpu_arm(args) -> None:
         torch.cuda.synchronize()
 
     stack = LayerStack(layers=args.layers, batch=args.batch, vocab=151936, rank=rank, world=world,
-                       device=device, seed=0)
+                       device=device, seed=0, fused=not args.unfused)
     # correctness before timing: one projection of this rank against the C oracle
     if rank == 0:
         from oracle import c_oracle, tq1_oracle as o
@@ -261,6 +265,8 @@ def run_gpu_arm(args) -> None:
     alg_bytes_all = alg_bytes_rank * world
     value = alg_bytes_all / (ms_per_step / 1e3) / 1e9
 
+    per_shape = measure_shapes(stack, device) if world == 1 else None
+
     # end-to-end through the public operator API with host buffers
     e2e = None
     if not args.skip_e2e:
@@ -297,6 +303,8 @@ def run_gpu_arm(args) -> None:
         }
         if e2e is not None:
             line["e2e"] = e2e
+        if per_shape is not None:
+            line["per_shape"] = per_shape
         if world == 1 and not args.skip_cpu_baseline:
             v, threads, reps, sec = time_cpu_layer(args.batch, budget_s=12.0, min_reps=3)
             line["cpu_baseline"] = {
@@ -308,6 +316,52 @@ def run_gpu_arm(args) -> None:
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def measure_shapes(stack, device, replays: int = 5):
+    """Stream regime per projection shape: the same projection of every layer back to back
+    (distinct weight buffers, far more than L2 in total), one CUDA graph per shape."""
+    import ctypes
+    import torch
+    from ternel_b200.format import check
+
+    lib = stack.lib
+    out = {}
+    seen = set()
+    for j, (name, n, k) in enumerate(stack.projections):
+        if (n, k) in seen:
+            continue
+        seen.add((n, k))
+
+        def run():
+            stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+            for layer in stack.weights:
+                check(lib.tq1_linear_f16(layer[j].data_ptr(), stack.inputs[k].data_ptr(),
+                                         stack.outputs[n].data_ptr(), 0, stack.batch, n, k,
+                                         stack.workspace.data_ptr(), stack.workspace_bytes, stream))
+
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            run()
+        for _ in range(2):
+            graph.replay()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(replays):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        us = start.elapsed_time(stop) * 1e3 / (replays * len(stack.weights))
+        alg = n * k // 128 * 28 + 2 * stack.batch * (n + k)
+        out[f"{n}x{k}"] = {"us_per_launch": us, "gbps": alg / us / 1e3, "ring_buffers": len(stack.weights)}
+    return out
 
 
 def measure_e2e(args, stack, device, world, barrier):

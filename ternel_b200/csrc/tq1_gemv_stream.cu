@@ -34,6 +34,7 @@
 // holds zeros for k-slots that belong to the other group, which keeps the two
 // groups' sums apart in one instruction.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "tq1_common.cuh"
 
@@ -59,21 +60,64 @@ constexpr uint32_t kLutBytes = 243 * 256;                     // 2 variants x 32
 constexpr uint32_t kWindowEnd = kLutWindowAddr + kLutBytes;
 constexpr uint32_t kRingBytes = kWarps * kStages * kUnitBytes;                   // 114688
 constexpr uint32_t kBtabBytes = kMaxChunksPerCta * 2 * kRegsPerSub * 32 * 4;     // 13824
-constexpr uint32_t kCarveBytes = kRingBytes + kBtabBytes + 16 * kMaxChunksPerCta * kChunkGroups +
-                                 8 * kWarps * kStages + 3 * 4 * kWarps;
+constexpr uint32_t kMbarBytes = 8 * (kWarps * kStages + 2);                        // per-warp stages + table barrier
+constexpr uint32_t kRedBytes = 3 * 4 * kWarps * kMaxChunksPerCta;                  // group max / sum / non-finite flags
+constexpr uint32_t kCarveBytes = kRingBytes + kBtabBytes + kMbarBytes + kRedBytes;
 static_assert(kCarveBytes + 1024 + 128 <= kLutWindowAddr, "buffers must end below the table's fixed address");
 constexpr uint32_t kMaxWaitSpins = 1u << 22;
 
-struct GroupInfo {
-    int sum;          // sum of the group's fixed-point activations
-    float pow2;       // 2^(E-21)
-    int nonfinite;    // the group holds a NaN or an Inf
-    int pad;
+// Optional phase timers (build with -DTQ1_PHASE_TIMERS): the last warp of every CTA records
+// %globaltimer at each phase boundary; tq1_debug_read_phases() copies them out.
+#ifdef TQ1_PHASE_TIMERS
+constexpr int kPhases = 10;
+__device__ unsigned long long g_phase_log[256 * kPhases];
+__device__ __forceinline__ void phase_mark(int idx) {
+    if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == kWarps - 1 && blockIdx.x < 256) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_phase_log[blockIdx.x * kPhases + idx] = t;
+    }
+}
+#define PHASE(i) phase_mark(i)
+#else
+#define PHASE(i)
+#endif
+
+// The decode table as it sits in shared memory, built at compile time: entry v (a code
+// byte) holds the PRMT selector nibbles of trits c0..c3 in its low half and trit c4 in
+// byte 2 (variant A) or byte 3 (variant B); each variant is replicated for the 32 lanes
+// so that lane i always reads bank i. A CTA fetches the image with one bulk copy.
+struct LutImage {
+    uint32_t w[243 * 64];
 };
+constexpr LutImage make_lut_image() {
+    LutImage img{};
+    for (int v = 0; v < 243; ++v) {
+        uint32_t c[5] = {0, 0, 0, 0, 0};
+        int t = v;
+        for (int d = 0; d < 5; ++d) { c[d] = (uint32_t)(t % 3); t /= 3; }
+        const uint32_t low = c[0] | (c[1] << 4) | (c[2] << 8) | (c[3] << 12);
+        for (int l = 0; l < 32; ++l) {
+            img.w[v * 64 + l] = low | (c[4] << 16);
+            img.w[v * 64 + 32 + l] = low | (c[4] << 24);
+        }
+    }
+    return img;
+}
+__device__ __align__(128) const LutImage g_lut_image = make_lut_image();
+static_assert(sizeof(LutImage) == kLutBytes, "table image size");
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t d;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// a + b issued as an integer multiply-add, which runs on the FMA pipe and leaves the
+// (half-rate) integer ALU to the byte permutes
+__device__ __forceinline__ uint32_t add_fma_pipe(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mad.lo.u32 %0, %1, 1, %2;" : "=r"(d) : "r"(a), "r"(b));
     return d;
 }
 
@@ -116,6 +160,11 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -147,11 +196,11 @@ __device__ __forceinline__ void decode_stream(uint32_t wa, uint32_t wb, uint32_t
     for (int s = 0; s < 14; ++s) r[s] = prmt(pool, 0u, e[s]);       // nibbles c0..c3 -> four u8 codes
 #pragma unroll
     for (int u = 0; u < 3; ++u) {
-        const uint32_t x = e[4 * u] + e[4 * u + 1];                  // bytes 2,3 = c4 of slots 4u, 4u+1
-        const uint32_t y = e[4 * u + 2] + e[4 * u + 3];
+        const uint32_t x = add_fma_pipe(e[4 * u], e[4 * u + 1]);     // bytes 2,3 = c4 of slots 4u, 4u+1
+        const uint32_t y = add_fma_pipe(e[4 * u + 2], e[4 * u + 3]);
         r[14 + u] = prmt(x, y, 0x7632);
     }
-    r[17] = prmt(e[12] + e[13], 0u, 0x4432);
+    r[17] = prmt(add_fma_pipe(e[12], e[13]), 0u, 0x4432);
 }
 
 // FP32 fallback for one block (row-major canonical bytes in shared memory) against
@@ -179,16 +228,13 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
                        unsigned *__restrict__ status) {
     extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t window = (uint32_t)__cvta_generic_to_shared(smem);   // window address of smem[0]
-    // carve-up: [ring | btab | ginfo | mbarriers] then the table at a fixed window address
-    unsigned char *ring = smem;                                          // 1024-aligned is plenty for TMA (16 B)
+    // carve-up: [ring | btab | mbarriers | reduction scratch], then the table at a fixed window address
+    unsigned char *ring = smem;
     uint32_t *btab = reinterpret_cast<uint32_t *>(smem + kRingBytes);
-    GroupInfo *ginfo = reinterpret_cast<GroupInfo *>(smem + kRingBytes + kBtabBytes);
-    uint64_t *mbars = reinterpret_cast<uint64_t *>(smem + kRingBytes + kBtabBytes +
-                                                   sizeof(GroupInfo) * kMaxChunksPerCta * kChunkGroups);
-    float *red_max = reinterpret_cast<float *>(mbars + kWarps * kStages);
-    int *red_sum = reinterpret_cast<int *>(red_max + kWarps);
-    int *red_bad = red_sum + kWarps;
-    unsigned char *lut = smem + (kLutWindowAddr - window);
+    uint64_t *mbars = reinterpret_cast<uint64_t *>(smem + kRingBytes + kBtabBytes);
+    float *red_max = reinterpret_cast<float *>(smem + kRingBytes + kBtabBytes + kMbarBytes);   // [chunk][warp]
+    int *red_sum = reinterpret_cast<int *>(red_max + kMaxChunksPerCta * kWarps);
+    int *red_bad = red_sum + kMaxChunksPerCta * kWarps;
     if (window + kCarveBytes > kLutWindowAddr) {      // the fixed-address table would overlap the buffers
         if (threadIdx.x == 0) atomicExch(status, 2u);
         return;
@@ -198,127 +244,145 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     const int lane = tid & 31;
     const int warp = tid >> 5;
 
-    // ---- unit range of this CTA and of this warp -------------------------------------------
-    const long long total_units = (long long)tiles * chunks;
-    const long long cta_begin = total_units * blockIdx.x / gridDim.x;
-    const long long cta_end = total_units * (blockIdx.x + 1) / gridDim.x;
-    const long long cta_units = cta_end - cta_begin;
-    const long long u_begin = cta_begin + cta_units * warp / kWarps;
-    const long long u_end = cta_begin + cta_units * (warp + 1) / kWarps;
-    const int chunk_lo = cta_units > 0 ? (int)(cta_begin / tiles) : 0;
-    const int chunk_hi = cta_units > 0 ? (int)((cta_end - 1) / tiles) : -1;
+    PHASE(0);
+    // ---- unit range of this CTA and of this warp (units are numbered chunk-major) ----------------
+    const int total_units = tiles * chunks;
+    const int cta_begin = (int)((long long)total_units * blockIdx.x / gridDim.x);
+    const int cta_end = (int)((long long)total_units * (blockIdx.x + 1) / gridDim.x);
+    const int cta_units = cta_end - cta_begin;
+    const int u_begin = cta_begin + ((cta_units * warp) >> 4);
+    const int u_end = cta_begin + ((cta_units * (warp + 1)) >> 4);
+    const int n_units = u_end - u_begin;
+    const int chunk_lo = cta_units > 0 ? cta_begin / tiles : 0;
+    const int chunk_hi = cta_units > 0 ? (cta_end - 1) / tiles : -1;
+    const int c_first = u_begin / tiles;
+    const int t_first = u_begin - c_first * tiles;
 
-    // ---- prologue 1: mbarriers, the decode table ------------------------------------------------
+    // ---- first of all, get this warp's weight bytes (and the decode table) moving -----------------
+    const uint32_t ring_warp = window + (uint32_t)(warp * kStages * kUnitBytes);
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&mbars[warp * kStages]);
+    const uint32_t lut_bar = (uint32_t)__cvta_generic_to_shared(&mbars[kWarps * kStages]);
+    int issue_c = c_first, issue_t = t_first, issued = 0;      // next unit to request (lane 0 only)
+    auto issue_next = [&]() {
+        const int s = issued % kStages;
+        mbar_expect_tx(bar0 + 8u * s, kUnitBytes);
+        tma_load_2d(ring_warp + (uint32_t)(s * kUnitBytes), &wmap, issue_c * kChunkBytes, issue_t * kTileRows,
+                    bar0 + 8u * s);
+        ++issued;
+        if (++issue_t == tiles) { issue_t = 0; ++issue_c; }
+    };
     if (lane == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init((uint32_t)__cvta_generic_to_shared(&mbars[warp * kStages + s]), 1);
+        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8u * s, 1);
+        if (warp == 0) mbar_init(lut_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (warp == 0) {
+            mbar_expect_tx(lut_bar, kLutBytes);
+            bulk_load(kLutWindowAddr, &g_lut_image, kLutBytes, lut_bar);
+        }
+        while (issued < kStages - 1 && issued < n_units) issue_next();
     }
-    for (int i = tid; i < 243 * 2; i += kThreads) {
-        const int v = i >> 1, variant = i & 1;
-        uint32_t c[5], t = v;
-        for (int d = 0; d < 5; ++d) { c[d] = t % 3u; t /= 3u; }
-        const uint32_t entry = c[0] | (c[1] << 4) | (c[2] << 8) | (c[3] << 12) | (c[4] << (variant ? 24 : 16));
-        uint4 *dst = reinterpret_cast<uint4 *>(lut + v * 256 + variant * 128);
-        const uint4 val = make_uint4(entry, entry, entry, entry);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) dst[k] = val;
-    }
-    for (int i = tid; i < (int)(kBtabBytes / 4); i += kThreads) btab[i] = 0u;
-    __syncthreads();
+    // Let the next kernel in the stream start its own prologue as SMs free up, then wait until
+    // everything before this kernel has finished before touching activations or the workspace.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    PHASE(1);
 
-    // ---- prologue 2: activation digits for the chunks this CTA touches ---------------------------
-    // one thread per activation: 512 threads = one chunk per pass
-    for (int c = chunk_lo; c <= chunk_hi; ++c) {
-        const int cl = c - chunk_lo;
-        const int k = c * (kChunkGroups * kGroup) + tid;
-        const float v = __half2float(x[k]);
-        const float a = fabsf(v);
-        const bool bad = !(a <= 65504.0f);                 // NaN or Inf
-        float m = bad ? 0.0f : a;
-        int anybad = bad;
+    // activations of the (at most three) chunks this CTA touches: one thread per activation
+    float xv[kMaxChunksPerCta];
+#pragma unroll
+    for (int cl = 0; cl < kMaxChunksPerCta; ++cl)
+        xv[cl] = chunk_lo + cl <= chunk_hi
+                     ? __half2float(__ldg(x + (size_t)(chunk_lo + cl) * (kChunkGroups * kGroup) + tid))
+                     : 0.0f;
+    for (int i = tid; i < (int)(kBtabBytes / 16); i += kThreads)
+        reinterpret_cast<uint4 *>(btab)[i] = make_uint4(0u, 0u, 0u, 0u);
+
+    // ---- activation digits: group maximum, fixed point, three signed byte planes ------------------
+    bool bad[kMaxChunksPerCta];
+    const int n_chunks_cta = chunk_hi - chunk_lo + 1;
+#pragma unroll
+    for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
+        if (cl >= n_chunks_cta) break;
+        const float a = fabsf(xv[cl]);
+        bad[cl] = !(a <= 65504.0f);                        // NaN or Inf
+        float m = bad[cl] ? 0.0f : a;
+        int anybad = bad[cl];
+#pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
             anybad |= __shfl_xor_sync(0xffffffffu, anybad, o);
         }
-        if (lane == 0) { red_max[warp] = m; red_bad[warp] = anybad; }
-        __syncthreads();
-        const int gw = warp & ~3;                          // the four warps of this thread's group
-        m = fmaxf(fmaxf(red_max[gw], red_max[gw + 1]), fmaxf(red_max[gw + 2], red_max[gw + 3]));
-        anybad = red_bad[gw] | red_bad[gw + 1] | red_bad[gw + 2] | red_bad[gw + 3];
-        // 2^E <= m < 2^(E+1); fixed point xi = round(v * 2^(21-E)), |xi| <= 2^22
-        const int e_biased = m > 0.0f ? (int)(__float_as_uint(m) >> 23) : 127;
-        const float up = __uint_as_float((uint32_t)(127 + 21 + 127 - e_biased) << 23);     // 2^(21-E)
-        const float down = __uint_as_float((uint32_t)(e_biased - 21) << 23);               // 2^(E-21)
-        const int xi = bad ? 0 : __float2int_rn(v * up);
-        const int d0 = (xi << 24) >> 24;
-        const int r1 = (xi - d0) >> 8;
-        const int d1 = (r1 << 24) >> 24;
-        const int d2 = (r1 - d1) >> 8;
-        int s = xi;
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (lane == 0) red_sum[warp] = s;
-        // scatter the three digits into the B-fragment table
+        if (lane == 0) { red_max[cl * kWarps + warp] = m; red_bad[cl * kWarps + warp] = anybad; }
+    }
+    __syncthreads();
+    PHASE(2);
+    {
+        // where this thread's activation sits in the B fragments (same for every chunk)
         const int gi = tid >> 7;                           // group within the chunk
         const int el = tid & 127;
-        const int j = el < 125 ? el / 5 : 25;
-        const int i = el < 125 ? el - 5 * j : el - 125;
-        const int h = j < 14 ? 0 : 1;
-        const int slot = h ? j - 12 : j;
+        const int j = el < 125 ? el / 5 : 25;              // code byte
+        const int i = el < 125 ? el - 5 * j : el - 125;    // trit within the byte
+        const int hh = j < 14 ? 0 : 1;                     // which half-block lane decodes it
+        const int slot = hh ? j - 12 : j;
         const int reg = i < 4 ? slot : 14 + (slot >> 2);
         const int pos = i < 4 ? i : (slot & 3);
-        const int sub = gi & 1, cls = gi >> 1;
-        unsigned char *base = reinterpret_cast<unsigned char *>(btab) +
-                              (((cl * 2 + sub) * kRegsPerSub + reg) * 32) * 4 + pos;
-        const int qq = 2 * cls + h;
-        base[(4 * (0 + 4 * cls) + qq) * 4] = (unsigned char)d0;
-        base[(4 * (1 + 4 * cls) + qq) * 4] = (unsigned char)d1;
-        base[(4 * (2 + 4 * cls) + qq) * 4] = (unsigned char)d2;
-        __syncthreads();
-        if (tid < kChunkGroups) {
-            GroupInfo info;
-            info.sum = red_sum[4 * tid] + red_sum[4 * tid + 1] + red_sum[4 * tid + 2] + red_sum[4 * tid + 3];
-            const float gm = fmaxf(fmaxf(red_max[4 * tid], red_max[4 * tid + 1]),
-                                   fmaxf(red_max[4 * tid + 2], red_max[4 * tid + 3]));
-            const int eb = gm > 0.0f ? (int)(__float_as_uint(gm) >> 23) : 127;
-            info.pow2 = __uint_as_float((uint32_t)(eb - 21) << 23);
-            info.nonfinite = red_bad[4 * tid] | red_bad[4 * tid + 1] | red_bad[4 * tid + 2] | red_bad[4 * tid + 3];
-            info.pad = 0;
-            ginfo[cl * kChunkGroups + tid] = info;
+        const int sub = gi & 1, cg = gi >> 1;
+        const int owner = 4 * (4 * cg) + 2 * cg + hh;      // B lane of digit plane 0; planes 1,2 are +4, +8
+        const int gw = warp & ~3;                          // the four warps of this thread's group
+#pragma unroll
+        for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
+            if (cl >= n_chunks_cta) break;
+            const float *rm = red_max + cl * kWarps + gw;
+            const float m = fmaxf(fmaxf(rm[0], rm[1]), fmaxf(rm[2], rm[3]));
+            // 2^E <= m < 2^(E+1); fixed point xi = round(v * 2^(21-E)), |xi| <= 2^22
+            const int e_biased = m > 0.0f ? (int)(__float_as_uint(m) >> 23) : 127;
+            const float up = __uint_as_float((uint32_t)(275 - e_biased) << 23);            // 2^(21-E)
+            const int xi = bad[cl] ? 0 : __float2int_rn(xv[cl] * up);
+            const int d0 = (xi << 24) >> 24;
+            const int r1 = (xi - d0) >> 8;
+            const int d1 = (r1 << 24) >> 24;
+            const int d2 = (r1 - d1) >> 8;
+            int s = xi;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0) red_sum[cl * kWarps + warp] = s;
+            unsigned char *base = reinterpret_cast<unsigned char *>(btab) +
+                                  ((((cl * 2 + sub) * kRegsPerSub + reg) * 32 + owner) * 4) + pos;
+            base[0] = (unsigned char)d0;
+            base[16] = (unsigned char)d1;
+            base[32] = (unsigned char)d2;
         }
-        (void)down;
-        __syncthreads();
     }
+    __syncthreads();
+    PHASE(3);
+    if (n_units <= 0) return;
 
-    if (u_begin >= u_end) return;
+    // the decode table must have landed
+    {
+        uint32_t spins = 0;
+        while (!mbar_try_wait(lut_bar, 0)) {
+            if (++spins > kMaxWaitSpins) {
+                if (lane == 0) atomicExch(status, 1u);
+                return;
+            }
+        }
+    }
 
     // ---- per-warp streaming loop ---------------------------------------------------------------------
     const int g = lane >> 2, q = lane & 3;
     const int cls = q >> 1, h = q & 1;
     const uint32_t lane_base = kLutWindowAddr + (uint32_t)lane * 4u;
-    const uint32_t ring_warp = window + (uint32_t)(warp * kStages * kUnitBytes);
-    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&mbars[warp * kStages]);
-    const int n_units = (int)(u_end - u_begin);
-
-    auto issue = [&](int i) {       // lane 0 only
-        const long long u = u_begin + i;
-        const int c = (int)(u / tiles), t = (int)(u % tiles);
-        const int s = i % kStages;
-        mbar_expect_tx(bar0 + 8u * s, kUnitBytes);
-        tma_load_2d(ring_warp + (uint32_t)(s * kUnitBytes), &wmap, c * kChunkBytes, t * kTileRows, bar0 + 8u * s);
-    };
-    if (lane == 0)
-        for (int i = 0; i < kStages - 1 && i < n_units; ++i) issue(i);
 
     uint32_t breg[2][kRegsPerSub];
     int gsum[2];
     float gpow[2];
     int gbad[2];
     int cur_chunk = -1;
+    int c = c_first, t = t_first;
 
     for (int i = 0; i < n_units; ++i) {
-        const long long u = u_begin + i;
-        const int c = (int)(u / tiles), t = (int)(u % tiles);
-        if (c != cur_chunk) {       // (re)load the B fragments of this K chunk
+        if (c != cur_chunk) {       // (re)load the B fragments and the group constants of this K chunk
             cur_chunk = c;
             const int cl = c - chunk_lo;
 #pragma unroll
@@ -326,10 +390,12 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
 #pragma unroll
                 for (int r = 0; r < kRegsPerSub; ++r)
                     breg[sub][r] = btab[((cl * 2 + sub) * kRegsPerSub + r) * 32 + lane];
-                const GroupInfo info = ginfo[cl * kChunkGroups + sub + 2 * cls];
-                gsum[sub] = info.sum;
-                gpow[sub] = info.pow2;
-                gbad[sub] = info.nonfinite;
+                const int w4 = cl * kWarps + 4 * (sub + 2 * cls);          // the group's four warps
+                gsum[sub] = red_sum[w4] + red_sum[w4 + 1] + red_sum[w4 + 2] + red_sum[w4 + 3];
+                const float gm = fmaxf(fmaxf(red_max[w4], red_max[w4 + 1]), fmaxf(red_max[w4 + 2], red_max[w4 + 3]));
+                const int eb = gm > 0.0f ? (int)(__float_as_uint(gm) >> 23) : 127;
+                gpow[sub] = __uint_as_float((uint32_t)(eb - 21) << 23);                    // 2^(E-21)
+                gbad[sub] = red_bad[w4] | red_bad[w4 + 1] | red_bad[w4 + 2] | red_bad[w4 + 3];
             }
         }
         const int s = i % kStages;
@@ -341,6 +407,7 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
                 return;
             }
         }
+        if (i == 0) PHASE(4);
         const uint32_t tile_addr = ring_warp + (uint32_t)(s * kUnitBytes);
         float acc1 = 0.0f, acc2 = 0.0f;             // rows g and g+8, this lane's two groups
 #pragma unroll
@@ -353,10 +420,19 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
             uint32_t r1[kRegsPerSub], r2[kRegsPerSub];
             decode_stream(w1a, w1b, w1c, w1d, lane_base, r1);
             decode_stream(w2a, w2b, w2c, w2d, lane_base, r2);
-            int acc[4] = {0, 0, 0, 0};
+            // three independent accumulator chains keep the tensor pipe's latency off the critical path
+            int accA[4] = {0, 0, 0, 0}, accB[4] = {0, 0, 0, 0}, accC[4] = {0, 0, 0, 0};
 #pragma unroll
-            for (int k = 0; k < kRegsPerSub / 2; ++k)
-                mma_u8s8(acc, r1[2 * k], r2[2 * k], r1[2 * k + 1], r2[2 * k + 1], breg[sub][2 * k], breg[sub][2 * k + 1]);
+            for (int k = 0; k < kRegsPerSub / 2; k += 3) {
+                mma_u8s8(accA, r1[2 * k], r2[2 * k], r1[2 * k + 1], r2[2 * k + 1], breg[sub][2 * k], breg[sub][2 * k + 1]);
+                mma_u8s8(accB, r1[2 * k + 2], r2[2 * k + 2], r1[2 * k + 3], r2[2 * k + 3], breg[sub][2 * k + 2],
+                         breg[sub][2 * k + 3]);
+                mma_u8s8(accC, r1[2 * k + 4], r2[2 * k + 4], r1[2 * k + 5], r2[2 * k + 5], breg[sub][2 * k + 4],
+                         breg[sub][2 * k + 5]);
+            }
+            int acc[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) acc[k] = accA[k] + accB[k] + accC[k];
             // columns: lane q=0 holds planes 0,1 of the first group, q=1 plane 2; q=2/3 the second group
             const int hi1 = __shfl_down_sync(0xffffffffu, acc[0], 1);
             const int hi2 = __shfl_down_sync(0xffffffffu, acc[2], 1);
@@ -377,39 +453,85 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
                 acc2 = fmaf(sc2, dot2, acc2);
             }
         }
-        // the stage is fully consumed (its words are in registers): refill it
+        // the stage consumed one iteration ago is free: refill it
         __syncwarp();
-        if (lane == 0 && i + kStages - 1 < n_units) issue(i + kStages - 1);
+        if (lane == 0 && issued < n_units) issue_next();
 
         // quad: lanes q=0 (groups 0,1) and q=2 (groups 2,3) -> chunk partial in lane q=0
         acc1 += __shfl_down_sync(0xffffffffu, acc1, 2);
         acc2 += __shfl_down_sync(0xffffffffu, acc2, 2);
-        const int row0 = t * kTileRows;
-        float *mine = partials + (size_t)c * tiles * kTileRows + row0;
         if (q == 0) {
+            float *mine = partials + ((size_t)c * tiles + t) * kTileRows;
             __stcg(mine + g, acc1);
             __stcg(mine + g + 8, acc2);
         }
-        __threadfence();
-        __syncwarp();
-        int prev = 0;
-        if (lane == 0) prev = atomicAdd(&counters[t], 1);
-        prev = __shfl_sync(0xffffffffu, prev, 0);
-        if (prev == chunks - 1) {       // this warp completed the row tile: fixed-order reduction
-            __threadfence();
-            if (lane < kTileRows) {
-                const int row = row0 + lane;
-                float total = 0.0f;
-                for (int cc = 0; cc < chunks; ++cc)
-                    total += __ldcg(partials + (size_t)cc * tiles * kTileRows + row);
-                if (row < N) {
-                    if (OUT_F32) static_cast<float *>(y)[row] = total;
-                    else static_cast<__half *>(y)[row] = __float2half_rn(total);
+        if (i == 0) PHASE(5);
+        if (++t == tiles) { t = 0; ++c; }
+    }
+
+    PHASE(6);
+    // ---- publish: one fence for all of this warp's partial sums, then one arrival per row tile -----
+    __threadfence();
+    __syncwarp();
+    PHASE(7);
+    for (int i0 = 0; i0 < n_units; i0 += 32) {
+        int last = 0;
+        if (i0 + lane < n_units) {
+            const int tt = (u_begin + i0 + lane) % tiles;
+            last = atomicAdd(&counters[tt], 1) == chunks - 1;
+        }
+        unsigned todo = __ballot_sync(0xffffffffu, last);
+        if (todo) __threadfence();
+        // This warp completed these row tiles; two are reduced per pass. Lane (ts, jj, rq) adds
+        // chunks jj, jj+4, jj+8, ... of rows 4rq..4rq+3 of tile slot ts in ascending order, then a
+        // fixed shuffle tree over jj: the order never depends on timing.
+        const int ts = lane >> 4, jj = (lane >> 2) & 3, rq = lane & 3;
+        const size_t stride = (size_t)tiles * kTileRows;
+        while (todo) {
+            const int b0 = __ffs(todo) - 1;
+            todo &= todo - 1;
+            int b1 = -1;
+            if (todo) { b1 = __ffs(todo) - 1; todo &= todo - 1; }
+            const int bit = ts ? b1 : b0;
+            const int tt = bit >= 0 ? (u_begin + i0 + bit) % tiles : 0;
+            float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (bit >= 0) {
+                const float *p = partials + (size_t)tt * kTileRows + 4 * rq;
+                for (int cc = jj; cc < chunks; cc += 32) {
+                    float4 v[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        v[k] = cc + 4 * k < chunks
+                                   ? __ldcg(reinterpret_cast<const float4 *>(p + (size_t)(cc + 4 * k) * stride))
+                                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        total.x += v[k].x; total.y += v[k].y; total.z += v[k].z; total.w += v[k].w;
+                    }
                 }
             }
-            if (lane == 0) counters[t] = 0;     // ready for the next call
+#pragma unroll
+            for (int o = 4; o < 16; o <<= 1) {
+                total.x += __shfl_xor_sync(0xffffffffu, total.x, o);
+                total.y += __shfl_xor_sync(0xffffffffu, total.y, o);
+                total.z += __shfl_xor_sync(0xffffffffu, total.z, o);
+                total.w += __shfl_xor_sync(0xffffffffu, total.w, o);
+            }
+            if (bit >= 0 && jj == 0) {
+                const int row = tt * kTileRows + 4 * rq;
+                const float out[4] = {total.x, total.y, total.z, total.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (row + k < N) {
+                        if (OUT_F32) static_cast<float *>(y)[row + k] = out[k];
+                        else static_cast<__half *>(y)[row + k] = __float2half_rn(out[k]);
+                    }
+                }
+                if (rq == 0) counters[tt] = 0;     // ready for the next call
+            }
         }
     }
+    PHASE(8);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -499,13 +621,33 @@ int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f
     const long long units = (long long)tiles * chunks;
     int grid = sm_count;
     if (units < grid) grid = (int)units;
-    if (y_f32)
-        kf<<<grid, kThreads, smem_bytes, stream>>>(map, x, y, N, K, tiles, chunks, counters, partials, status);
-    else
-        kh<<<grid, kThreads, smem_bytes, stream>>>(map, x, y, N, K, tiles, chunks, counters, partials, status);
-    cudaError_t err = cudaGetLastError();
+    // Programmatic dependent launch: the kernel's prologue (table fetch, first weight tiles) may
+    // overlap the tail of whatever precedes it in the stream; it waits (griddepcontrol.wait)
+    // before it reads activations or writes anything.
+    static const bool use_pdl = getenv("TQ1_DISABLE_PDL") == nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    const __half *xc = x;
+    cudaError_t err = y_f32 ? cudaLaunchKernelEx(&cfg, kf, map, xc, y, N, K, tiles, chunks, counters, partials, status)
+                            : cudaLaunchKernelEx(&cfg, kh, map, xc, y, N, K, tiles, chunks, counters, partials, status);
+    if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: launch");
+    err = cudaGetLastError();
     if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: launch");
     return TQ1_OK;
 }
 
 }  // namespace tq1
+
+#ifdef TQ1_PHASE_TIMERS
+extern "C" int tq1_debug_read_phases(unsigned long long *out, int ctas) {
+    return (int)cudaMemcpyFromSymbol(out, tq1::g_phase_log, sizeof(unsigned long long) * tq1::kPhases * ctas);
+}
+#endif

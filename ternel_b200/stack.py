@@ -34,10 +34,18 @@ class LayerShape:
     kv_heads: int = 8
     head_dim: int = 128
 
-    def projections(self) -> tuple[tuple[str, int, int], ...]:
-        """(name, N out, K in) in launch order."""
+    def projections(self, fused: bool = False) -> tuple[tuple[str, int, int], ...]:
+        """(name, N out, K in) in launch order.
+
+        ``fused`` stores q/k/v (same input) as one row-concatenated matrix and gate/up
+        likewise, as fused-QKV checkpoints do: the same bytes in four launches per layer
+        instead of seven.
+        """
         q = self.q_heads * self.head_dim
         kv = self.kv_heads * self.head_dim
+        if fused:
+            return (("qkv", q + 2 * kv, self.hidden), ("o", self.hidden, q),
+                    ("gate_up", 2 * self.ffn, self.hidden), ("down", self.hidden, self.ffn))
         return (
             ("q", q, self.hidden), ("k", kv, self.hidden), ("v", kv, self.hidden),
             ("o", self.hidden, q), ("gate", self.ffn, self.hidden), ("up", self.ffn, self.hidden),
@@ -75,14 +83,15 @@ class LayerStack:
 
     def __init__(self, *, layers: int, batch: int = 1, shape: LayerShape = LayerShape(),
                  vocab: int = 0, rank: int = 0, world: int = 1, device=None, seed: int = 0,
-                 group=None) -> None:
+                 group=None, fused: bool = False) -> None:
         self.layers, self.batch, self.shape = layers, batch, shape
         self.rank, self.world, self.group = rank, world, group
         self.device = torch.device(device if device is not None else "cuda")
         self.lib = _native.lib()
         gen = torch.Generator(device=self.device)
         gen.manual_seed(seed * 1000 + rank)
-        self.projections = shape.projections()
+        self.fused = fused
+        self.projections = shape.projections(fused)
         for _, n, _ in self.projections:
             if n % world or (n // world) % 16:
                 raise ValueError(f"{n} output rows do not shard evenly over {world} ranks")
