@@ -11,6 +11,7 @@ extern "C" {
 size_t tq1_linear_workspace_bytes(int M, int N, int K) {
     if (M <= 0 || N <= 0 || K <= 0 || K % kGroup) return 0;
     if (M == 1 && gemv_stream_shape_ok(N, K)) return gemv_stream_workspace_bytes(N, K);
+    if (gemm_tc_shape_ok(M, N, K)) return gemm_tc_workspace_bytes(M, N, K);
     return 0;
 }
 
@@ -32,6 +33,8 @@ int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (M == 1 && gemv_stream_supported(blocks, N, K))
         return launch_gemv_stream(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, N, K, workspace, s);
+    if (gemm_tc_supported(blocks, static_cast<const __half *>(x), M, N, K))
+        return launch_gemm_tc(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, workspace, s);
     return launch_gemv_rows(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, s);
 }
 

@@ -34,6 +34,13 @@ size_t gemv_stream_workspace_bytes(int N, int K);
 int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K,
                        void *workspace, cudaStream_t stream);
 
+// Batched linear (M >= 2) on tcgen05 tensor cores; needs K % 512 == 0 and 16-byte aligned pointers.
+bool gemm_tc_shape_ok(int M, int N, int K);
+bool gemm_tc_supported(const uint8_t *blocks, const __half *x, int M, int N, int K);
+size_t gemm_tc_workspace_bytes(int M, int N, int K);
+int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int M, int N, int K,
+                   void *workspace, cudaStream_t stream);
+
 // Five base-3 digits of a byte packed two bits each (digit i at bits 2i..2i+1).
 __host__ __device__ inline uint32_t trits_2bit(uint32_t byte) {
     uint32_t e = 0;

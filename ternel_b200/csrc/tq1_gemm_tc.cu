@@ -1,0 +1,521 @@
+// Batched linear (M >= 2 activation rows) for TQ1_G128 on sm_100a: trits are decoded into
+// FP16 shared-memory tiles that feed tcgen05.mma with FP32 accumulators in tensor memory.
+//
+// Stands in for the reference's prefill GEMM and small-batch kernels behind packed_matmul
+// (src/ternel_mlx/kernels.py:409-858,1287-1357; src/ternel_mlx/modules.py:425-457). As in
+// the reference's GEMM, the group scale is folded into the FP16 weight, which is exact:
+// (c-1)*s is -s, 0 or +s (src/ternel_mlx/kernels.py:435-440).
+//
+// One CTA computes a tile of 128 weight rows x NT activation rows over a range of K:
+//   D[n][m] = sum_k W[n][k] * x[m][k]      (A = W tile, B = x tile, both K-major FP16)
+//   warps 0-3  decode: thread r turns row r's 28-byte block into 128 FP16 values and writes
+//              them into the 128-byte-swizzled A tile; after the K loop the same warps read
+//              the accumulator (TMEM lane r = weight row r) and store y
+//   warp 4     TMA: packed weight bytes (box 128 rows x 112 B = 4 groups) and activation tiles
+//   warp 5     allocates tensor memory and issues tcgen05.mma (one elected lane)
+//
+// K order. Five trits per byte do not pair up in natural order, so inside every 128-wide
+// group the K axis is permuted to a decode-friendly order (position p -> column pi(p) below)
+// and the activations are permuted the same way once per call by a small pre-pass kernel;
+// a dot product does not care about the order of its terms.
+//   p = 4j+i   (j<25, i<4) : trit i of code byte j          (column 5j+i)
+//   p = 100,101,102        : the three tail trits           (columns 125,126,127)
+//   p = 103                : trit 4 of code byte 0          (column 4)
+//   p = 104+q  (q<24)      : trit 4 of code byte q+1        (column 5(q+1)+4)
+//
+// Small grids are filled by splitting K over gridDim.z; the FP32 partial tiles go to the
+// workspace and a second kernel adds them in ascending split order (deterministic).
+#include <cuda.h>
+#include <stdlib.h>
+
+#include "tq1_common.cuh"
+
+namespace tq1 {
+
+namespace {
+
+constexpr int kTileW = 128;                 // weight rows per tile (UMMA M)
+constexpr int kStagesG = 2;
+constexpr int kPackGroups = 4;
+constexpr int kPackBytes = kTileW * kPackGroups * kBlockBytes;     // 14336
+constexpr int kATileBytes = kTileW * kGroup * 2;                   // 32768: two 64-wide swizzle atoms
+constexpr int kLutBytesG = 243 * 256;                              // 8-byte entries x 32 lanes
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+__host__ __device__ constexpr int perm_column(int p) {
+    return p < 100 ? 5 * (p >> 2) + (p & 3) : p < 103 ? 125 + (p - 100) : p == 103 ? 4 : 5 * (p - 103) + 4;
+}
+
+// Decode table image: entry v = two words per lane.
+//   word0: PRMT selector of (trit0, trit1) in bits 0-15, the 8-bit selector of trit4 in byte 2 and byte 3
+//   word1: PRMT selector of (trit2, trit3) in bits 0-15
+// An 8-bit selector picks the two bytes of one FP16 value out of the pool
+// [0x00, s_lo, s_hi, s_hi ^ 0x80]: code 0 -> -s = (1,3), code 1 -> 0 = (0,0), code 2 -> +s = (1,2).
+struct GemmLutImage {
+    uint32_t w[243 * 64];
+};
+constexpr uint32_t sel8(uint32_t c) { return c == 0 ? 0x31u : c == 1 ? 0x00u : 0x21u; }
+constexpr GemmLutImage make_gemm_lut() {
+    GemmLutImage img{};
+    for (int v = 0; v < 243; ++v) {
+        uint32_t c[5] = {0, 0, 0, 0, 0};
+        int t = v;
+        for (int d = 0; d < 5; ++d) { c[d] = (uint32_t)(t % 3); t /= 3; }
+        const uint32_t w0 = sel8(c[0]) | (sel8(c[1]) << 8) | (sel8(c[4]) << 16) | (sel8(c[4]) << 24);
+        const uint32_t w1 = sel8(c[2]) | (sel8(c[3]) << 8);
+        for (int l = 0; l < 32; ++l) {
+            img.w[v * 64 + 2 * l] = w0;
+            img.w[v * 64 + 2 * l + 1] = w1;
+        }
+    }
+    return img;
+}
+__device__ __align__(128) const GemmLutImage g_gemm_lut = make_gemm_lut();
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// Bounded wait: returns false (after flagging *status) instead of hanging.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned *status) {
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if (++spins > kSpinLimit) {
+            atomicExch(status, 3u);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+
+struct GemmParams {
+    const __half *xperm;      // permuted activations [M][K]
+    void *y;                  // final output [M][N] (FP16/FP32) when splits == 1
+    float *partials;          // [splits][M][N] when splits > 1
+    unsigned *status;
+    int M, N, K;
+    int splits;
+    int y_f32;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
+                   const GemmParams prm) {
+    constexpr int kBTileBytes = NT * kGroup * 2;
+    constexpr int kTmemCols = NT < 32 ? 32 : NT;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // swizzled operand tiles must start on a 1024-byte boundary of the shared window
+    unsigned char *smem = smem_raw + ((1024u - ((uint32_t)__cvta_generic_to_shared(smem_raw) & 1023u)) & 1023u);
+    unsigned char *a_tiles = smem;                                       // kStagesG x 32 KiB, 1024-aligned
+    unsigned char *b_tiles = a_tiles + kStagesG * kATileBytes;           // kStagesG x NT*256
+    unsigned char *packed = b_tiles + kStagesG * kBTileBytes;            // 2 x 14336
+    unsigned char *lut = packed + 2 * kPackBytes;                        // 62208
+    uint64_t *bars = reinterpret_cast<uint64_t *>(lut + kLutBytesG);
+    // barrier indices
+    enum { FULL_A = 0, FULL_B = FULL_A + kStagesG, EMPTY = FULL_B + kStagesG, PACK_FULL = EMPTY + kStagesG,
+           PACK_EMPTY = PACK_FULL + 2, ACCUM = PACK_EMPTY + 2, LUT_BAR = ACCUM + 1, NUM_BARS = LUT_BAR + 1 };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NUM_BARS);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+
+    const int n0 = blockIdx.x * kTileW;                 // first weight row of the tile
+    const int m0 = blockIdx.y * NT;                     // first activation row
+    const int groups = prm.K / kGroup;
+    const int kb_begin = (int)((long long)groups * blockIdx.z / prm.splits);
+    const int kb_end = (int)((long long)groups * (blockIdx.z + 1) / prm.splits);
+    const int n_kb = kb_end - kb_begin;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStagesG; ++s) {
+            mbar_init(bar(FULL_A + s), 128);
+            mbar_init(bar(FULL_B + s), 1);
+            mbar_init(bar(EMPTY + s), 1);
+        }
+        for (int p = 0; p < 2; ++p) {
+            mbar_init(bar(PACK_FULL + p), 1);
+            mbar_init(bar(PACK_EMPTY + p), 128);
+        }
+        mbar_init(bar(ACCUM), 1);
+        mbar_init(bar(LUT_BAR), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(bar(LUT_BAR), kLutBytesG);
+        bulk_load((uint32_t)__cvta_generic_to_shared(lut), &g_gemm_lut, kLutBytesG, bar(LUT_BAR));
+    }
+    if (warp == 5) {        // tensor-memory allocation is a warp-wide operation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"((uint32_t)__cvta_generic_to_shared(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool ok = true;
+    if (warp == 4) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int pack_i = 0;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int kb = kb_begin + i;
+                if (i == 0 || (kb % kPackGroups) == 0) {        // a new 4-group chunk of packed bytes
+                    const int p = pack_i & 1;
+                    ok = mbar_wait(bar(PACK_EMPTY + p), ((uint32_t)(pack_i >> 1) & 1u) ^ 1u, prm.status);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(PACK_FULL + p), kPackBytes);
+                    tma_load_2d((uint32_t)__cvta_generic_to_shared(packed + p * kPackBytes), &wmap,
+                                (kb / kPackGroups) * (kPackGroups * kBlockBytes), n0, bar(PACK_FULL + p));
+                    ++pack_i;
+                }
+                const int s = i % kStagesG;
+                ok = mbar_wait(bar(EMPTY + s), ((uint32_t)(i / kStagesG) & 1u) ^ 1u, prm.status);
+                if (!ok) break;
+                mbar_expect_tx(bar(FULL_B + s), kBTileBytes);
+                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(b_tiles + s * kBTileBytes);
+                tma_load_2d(dst, &xmap, kb * kGroup, m0, bar(FULL_B + s));
+                tma_load_2d(dst + NT * 128, &xmap, kb * kGroup + 64, m0, bar(FULL_B + s));
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            // instruction descriptor: FP32 accumulate, FP16 A and B, both K-major, M = 128, N = NT
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(kTileW >> 4) << 24);
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % kStagesG;
+                const uint32_t ph = (uint32_t)(i / kStagesG) & 1u;
+                ok = mbar_wait(bar(FULL_A + s), ph, prm.status) && mbar_wait(bar(FULL_B + s), ph, prm.status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(a_tiles + s * kATileBytes);
+                const uint32_t b_addr = (uint32_t)__cvta_generic_to_shared(b_tiles + s * kBTileBytes);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {       // four K = 16 steps per 64-wide swizzle atom
+                        const uint64_t da = umma_desc(a_addr + half * (kTileW * 128) + j * 32);
+                        const uint64_t db = umma_desc(b_addr + half * (NT * 128) + j * 32);
+                        umma_f16(tmem_base, da, db, idesc, (i > 0 || half > 0 || j > 0) ? 1u : 0u);
+                    }
+                }
+                umma_commit(bar(EMPTY + s));            // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(bar(ACCUM));
+        }
+    } else {
+        // ------------------------------------------------------------------ decode (thread = weight row)
+        const int r = tid;                               // 0..127
+        ok = mbar_wait(bar(LUT_BAR), 0, prm.status);
+        const uint32_t lut_lane = (uint32_t)__cvta_generic_to_shared(lut) + (uint32_t)lane * 8u;
+        const uint32_t row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+        const uint32_t rx = (uint32_t)(r & 7);
+        int pack_i = -1;
+        for (int i = 0; i < n_kb && ok; ++i) {
+            const int kb = kb_begin + i;
+            if (i == 0 || (kb % kPackGroups) == 0) {
+                ++pack_i;
+                ok = mbar_wait(bar(PACK_FULL + (pack_i & 1)), (uint32_t)(pack_i >> 1) & 1u, prm.status);
+                if (!ok) break;
+            }
+            const int s = i % kStagesG;
+            ok = mbar_wait(bar(EMPTY + s), ((uint32_t)(i / kStagesG) & 1u) ^ 1u, prm.status);
+            if (!ok) break;
+
+            const uint32_t *blk = reinterpret_cast<const uint32_t *>(
+                packed + (pack_i & 1) * kPackBytes + (r * kPackGroups + (kb % kPackGroups)) * kBlockBytes);
+            uint32_t w[7];
+#pragma unroll
+            for (int k = 0; k < 7; ++k) w[k] = blk[k];
+            const uint32_t sbits = w[0] & 0xffffu;
+            const uint32_t pool = (sbits << 8) | (((sbits >> 8) ^ 0x80u) << 24);
+            // table entries of the 26 code bytes
+            uint32_t e0[26], e1[26];
+#pragma unroll
+            for (int j = 0; j < 26; ++j) {
+                const int bytepos = 2 + j;
+                const uint32_t byte = (w[bytepos >> 2] >> (8 * (bytepos & 3))) & 0xffu;
+                const uint32_t addr = lut_lane + (byte << 8);
+                asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(e0[j]), "=r"(e1[j]) : "r"(addr));
+            }
+            const uint32_t a_stage = (uint32_t)__cvta_generic_to_shared(a_tiles + s * kATileBytes) + row_off;
+            auto store_chunk = [&](int m, uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3) {
+                const uint32_t addr = a_stage + (uint32_t)((m >> 3) * (kTileW * 128)) + ((((uint32_t)m & 7u) ^ rx) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+                             : "memory");
+            };
+#pragma unroll
+            for (int m = 0; m < 12; ++m)
+                store_chunk(m, prmt(pool, 0u, e0[2 * m]), prmt(pool, 0u, e1[2 * m]),
+                            prmt(pool, 0u, e0[2 * m + 1]), prmt(pool, 0u, e1[2 * m + 1]));
+            // trit-4 pairs: selector byte 0 from entry a (its byte 2), byte 1 from entry b (its byte 3)
+            auto c4pair = [&](int ja, int jb) { return prmt(pool, 0u, prmt(e0[ja], e0[jb], 0x4472)); };
+            store_chunk(12, prmt(pool, 0u, e0[24]), prmt(pool, 0u, e1[24]), prmt(pool, 0u, e0[25]),
+                        prmt(pool, 0u, prmt(e1[25], e0[0], 0x4470)));       // (tail trit 2, trit 4 of byte 0)
+            store_chunk(13, c4pair(1, 2), c4pair(3, 4), c4pair(5, 6), c4pair(7, 8));
+            store_chunk(14, c4pair(9, 10), c4pair(11, 12), c4pair(13, 14), c4pair(15, 16));
+            store_chunk(15, c4pair(17, 18), c4pair(19, 20), c4pair(21, 22), c4pair(23, 24));
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
+            mbar_arrive(bar(FULL_A + s));
+            if ((kb % kPackGroups) == kPackGroups - 1 || i == n_kb - 1) mbar_arrive(bar(PACK_EMPTY + (pack_i & 1)));
+        }
+
+        // ------------------------------------------------------------------ epilogue (TMEM lane = weight row)
+        if (ok) ok = mbar_wait(bar(ACCUM), 0, prm.status);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int n = n0 + r;
+#pragma unroll 1
+            for (int c0 = 0; c0 < NT; c0 += 32) {
+                uint32_t v[32];
+                if (NT >= 32 || c0 == 0) {
+                    tmem_load32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                }
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const int m = m0 + c0 + c;
+                    if (c0 + c < NT && m < prm.M && n < prm.N) {
+                        const float f = __uint_as_float(v[c]);
+                        if (prm.splits > 1)
+                            prm.partials[((size_t)blockIdx.z * prm.M + m) * prm.N + n] = f;
+                        else if (prm.y_f32)
+                            static_cast<float *>(prm.y)[(size_t)m * prm.N + n] = f;
+                        else
+                            static_cast<__half *>(prm.y)[(size_t)m * prm.N + n] = __float2half_rn(f);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                     : "memory");
+    }
+}
+
+// x' = x with the K axis of every group permuted to the decode order.
+__global__ void tq1_permute_x_kernel(const __half *__restrict__ x, __half *__restrict__ xp, long long total) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int p = (int)(i & 127);
+    xp[i] = x[i - p + perm_column(p)];
+}
+
+// y[m][n] = sum over splits in ascending order.
+__global__ void tq1_splitk_reduce_kernel(const float *__restrict__ partials, void *__restrict__ y, int y_f32,
+                                         long long mn, int splits) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= mn) return;
+    float total = 0.0f;
+    for (int s = 0; s < splits; ++s) total += partials[(size_t)s * mn + i];
+    if (y_f32) static_cast<float *>(y)[i] = total;
+    else static_cast<__half *>(y)[i] = __float2half_rn(total);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn gemm_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
+
+int pick_splits(int M, int N, int K) {
+    const int nt = token_tile(M);
+    const long long tiles = (long long)((N + kTileW - 1) / kTileW) * ((M + nt - 1) / nt);
+    const int groups = K / kGroup;
+    int splits = 1;
+    if (tiles < 148) {
+        splits = (int)((148 + tiles - 1) / tiles);
+        const int max_splits = groups / 8 > 0 ? groups / 8 : 1;      // at least 8 groups per split
+        if (splits > max_splits) splits = max_splits;
+        if (splits > 32) splits = 32;
+    }
+    return splits;
+}
+
+size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+template <int NT>
+size_t gemm_smem_bytes() {
+    return (size_t)kStagesG * kATileBytes + (size_t)kStagesG * NT * kGroup * 2 + 2 * kPackBytes + kLutBytesG + 256 + 1024;
+}
+
+template <int NT>
+int launch_nt(const CUtensorMap &wmap, const CUtensorMap &xmap, const GemmParams &prm, dim3 grid, cudaStream_t stream) {
+    auto kern = tq1_gemm_tc_kernel<NT>;
+    static bool attr_set = false;
+    const size_t smem = gemm_smem_bytes<NT>();
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(e, "tq1_linear_f16: shared memory opt-in (GEMM)");
+        attr_set = true;
+    }
+    kern<<<grid, kGemmThreads, smem, stream>>>(wmap, xmap, prm);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: GEMM launch");
+    return TQ1_OK;
+}
+
+}  // namespace
+
+bool gemm_tc_shape_ok(int M, int N, int K) {
+    return M >= 2 && N >= 1 && K % (kPackGroups * kGroup) == 0;
+}
+
+bool gemm_tc_supported(const uint8_t *blocks, const __half *x, int M, int N, int K) {
+    return gemm_tc_shape_ok(M, N, K) && (reinterpret_cast<uintptr_t>(blocks) & 15) == 0 &&
+           (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+}
+
+size_t gemm_tc_workspace_bytes(int M, int N, int K) {
+    const int splits = pick_splits(M, N, K);
+    size_t bytes = 256 + align256((size_t)M * K * sizeof(__half));
+    if (splits > 1) bytes += align256((size_t)splits * M * N * sizeof(float));
+    return bytes;
+}
+
+int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int M, int N, int K,
+                   void *workspace, cudaStream_t stream) {
+    EncodeTiledFn encode = gemm_encode_fn();
+    if (!encode) return fail(TQ1_ERR_CUDA, "tq1_linear_f16: cuTensorMapEncodeTiled is unavailable");
+    unsigned char *ws = static_cast<unsigned char *>(workspace);
+    unsigned *status = reinterpret_cast<unsigned *>(ws);
+    __half *xperm = reinterpret_cast<__half *>(ws + 256);
+    float *partials = reinterpret_cast<float *>(ws + 256 + align256((size_t)M * K * sizeof(__half)));
+    const int nt = token_tile(M);
+    const int splits = pick_splits(M, N, K);
+
+    const long long total = (long long)M * K;
+    tq1_permute_x_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, xperm, total);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: activation permute launch");
+
+    CUtensorMap wmap, xmap;
+    {
+        const cuuint64_t row_bytes = (cuuint64_t)(K / kGroup) * kBlockBytes;
+        const cuuint64_t dims[2] = {row_bytes, (cuuint64_t)N};
+        const cuuint64_t strides[1] = {row_bytes};
+        const cuuint32_t box[2] = {kPackGroups * kBlockBytes, kTileW};
+        const cuuint32_t estr[2] = {1, 1};
+        CUresult res = encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(blocks), dims, strides,
+                              box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (res != CUDA_SUCCESS) return fail(TQ1_ERR_CUDA, "tq1_linear_f16: weight tensor map failed (%d)", (int)res);
+    }
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+        const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(__half)};
+        const cuuint32_t box[2] = {64, (cuuint32_t)nt};
+        const cuuint32_t estr[2] = {1, 1};
+        CUresult res = encode(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xperm, dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (res != CUDA_SUCCESS)
+            return fail(TQ1_ERR_CUDA, "tq1_linear_f16: activation tensor map failed (%d)", (int)res);
+    }
+    GemmParams prm;
+    prm.xperm = xperm;
+    prm.y = y;
+    prm.partials = partials;
+    prm.status = status;
+    prm.M = M;
+    prm.N = N;
+    prm.K = K;
+    prm.splits = splits;
+    prm.y_f32 = y_f32 ? 1 : 0;
+    dim3 grid((unsigned)((N + kTileW - 1) / kTileW), (unsigned)((M + nt - 1) / nt), (unsigned)splits);
+    int rc = nt == 16 ? launch_nt<16>(wmap, xmap, prm, grid, stream)
+           : nt == 32 ? launch_nt<32>(wmap, xmap, prm, grid, stream)
+           : nt == 64 ? launch_nt<64>(wmap, xmap, prm, grid, stream)
+                      : launch_nt<128>(wmap, xmap, prm, grid, stream);
+    if (rc != TQ1_OK) return rc;
+    if (splits > 1) {
+        const long long mn = (long long)M * N;
+        tq1_splitk_reduce_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, stream>>>(partials, y, prm.y_f32, mn, splits);
+        err = cudaGetLastError();
+        if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: split-K reduce launch");
+    }
+    return TQ1_OK;
+}
+
+}  // namespace tq1
