@@ -48,6 +48,7 @@ def parse_args():
                    help="seven launches per layer (q,k,v,o,gate,up,down) instead of four (qkv,o,gate_up,down)")
     p.add_argument("--skip-cpu-baseline", action="store_true")
     p.add_argument("--skip-e2e", action="store_true")
+    p.add_argument("--skip-batched", action="store_true", help="skip the small-batch and prefill side measurements")
     return p.parse_args()
 
 
@@ -266,6 +267,7 @@ def run_gpu_arm(args) -> None:
     value = alg_bytes_all / (ms_per_step / 1e3) / 1e9
 
     per_shape = measure_shapes(stack, device) if world == 1 else None
+    batched = measure_batched(device) if world == 1 and not args.skip_batched else None
 
     # end-to-end through the public operator API with host buffers
     e2e = None
@@ -305,6 +307,8 @@ def run_gpu_arm(args) -> None:
             line["e2e"] = e2e
         if per_shape is not None:
             line["per_shape"] = per_shape
+        if batched is not None:
+            line["batched"] = batched
         if world == 1 and not args.skip_cpu_baseline:
             v, threads, reps, sec = time_cpu_layer(args.batch, budget_s=12.0, min_reps=3)
             line["cpu_baseline"] = {
@@ -361,6 +365,56 @@ def measure_shapes(stack, device, replays: int = 5):
         us = start.elapsed_time(stop) * 1e3 / (replays * len(stack.weights))
         alg = n * k // 128 * 28 + 2 * stack.batch * (n + k)
         out[f"{n}x{k}"] = {"us_per_launch": us, "gbps": alg / us / 1e3, "ring_buffers": len(stack.weights)}
+    return out
+
+
+def measure_batched(device, replays: int = 3):
+    """Side measurements of the batched kernels: small batch (M = 2..16, HBM-bound, GB/s of packed
+    weights) and prefill (M = 512, 2048, tensor-bound, TFLOP/s), each over a ring of distinct weights."""
+    import ctypes
+    import torch
+    from ternel_b200 import _native
+    from ternel_b200.format import check
+    from ternel_b200.stack import random_blocks_device
+
+    lib = _native.lib()
+    gen = torch.Generator(device=device)
+    gen.manual_seed(123)
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peak_tf = float(json.loads(peaks_path.read_text()).get("bf16_tflops", 1590.0)) if peaks_path.exists() else 1590.0
+    out = {"small_batch": {}, "prefill": {}, "tensor_peak_tflops": peak_tf}
+    for n, k in ((17408, 5120), (5120, 17408)):
+        ring = [random_blocks_device(n, k, gen, device) for _ in range(14)]     # 14 x 19.5 MB > 2 x L2
+        for m in (2, 4, 8, 16, 512, 2048):
+            x = torch.randn((m, k), generator=gen, device=device).to(torch.float16)
+            y = torch.empty((m, n), dtype=torch.float16, device=device)
+            ws_bytes = lib.tq1_linear_workspace_bytes(m, n, k)
+            ws = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=device)
+
+            def run():
+                stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+                for w in ring:
+                    check(lib.tq1_linear_f16(w.data_ptr(), x.data_ptr(), y.data_ptr(), 0, m, n, k,
+                                             ws.data_ptr(), ws_bytes, stream))
+
+            for _ in range(2):
+                run()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(replays):
+                run()
+            stop.record()
+            torch.cuda.synchronize()
+            us = start.elapsed_time(stop) * 1e3 / (replays * len(ring))
+            if m <= 16:
+                alg = n * k // 128 * 28 + 2 * m * (n + k)
+                out["small_batch"][f"M{m}_{n}x{k}"] = {"us": us, "gbps": alg / us / 1e3}
+            else:
+                tf = 2.0 * m * n * k / us / 1e6
+                out["prefill"][f"M{m}_{n}x{k}"] = {"us": us, "tflops": tf, "frac_of_measured_peak": tf / peak_tf}
+            del x, y, ws
+        del ring
     return out
 
 
