@@ -16,6 +16,14 @@ constexpr int kFullBytes = 25;
 constexpr int kMaxFull = 242;
 constexpr int kMaxTail = 26;
 
+// Workspace layout shared by every linear kernel: [status word, 256 B][arrival counters, 64 KiB]
+// [kernel-specific scratch]. Only the counter region must be zero between calls, and no kernel
+// writes anything else there, so calls of any shape and kind can share one workspace.
+constexpr size_t kWsStatusBytes = 256;
+constexpr int kWsMaxCounters = 16384;
+constexpr size_t kWsCounterBytes = (size_t)kWsMaxCounters * sizeof(int);
+constexpr size_t kWsScratchOffset = kWsStatusBytes + kWsCounterBytes;
+
 // Records a message for tq1_last_error() and returns `code`.
 int fail(int code, const char *fmt, ...);
 int cuda_fail(cudaError_t err, const char *what);

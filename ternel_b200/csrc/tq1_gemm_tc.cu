@@ -449,7 +449,7 @@ bool gemm_tc_supported(const uint8_t *blocks, const __half *x, int M, int N, int
 
 size_t gemm_tc_workspace_bytes(int M, int N, int K) {
     const int splits = pick_splits(M, N, K);
-    size_t bytes = 256 + align256((size_t)M * K * sizeof(__half));
+    size_t bytes = kWsScratchOffset + align256((size_t)M * K * sizeof(__half));
     if (splits > 1) bytes += align256((size_t)splits * M * N * sizeof(float));
     return bytes;
 }
@@ -460,8 +460,8 @@ int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, 
     if (!encode) return fail(TQ1_ERR_CUDA, "tq1_linear_f16: cuTensorMapEncodeTiled is unavailable");
     unsigned char *ws = static_cast<unsigned char *>(workspace);
     unsigned *status = reinterpret_cast<unsigned *>(ws);
-    __half *xperm = reinterpret_cast<__half *>(ws + 256);
-    float *partials = reinterpret_cast<float *>(ws + 256 + align256((size_t)M * K * sizeof(__half)));
+    __half *xperm = reinterpret_cast<__half *>(ws + kWsScratchOffset);
+    float *partials = reinterpret_cast<float *>(ws + kWsScratchOffset + align256((size_t)M * K * sizeof(__half)));
     const int nt = token_tile(M);
     const int splits = pick_splits(M, N, K);
 

@@ -552,12 +552,9 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// Workspace layout: [status word, 256 B][arrival counters, fixed 64 KiB][per-chunk partial sums].
-// The counter region has a fixed size so that calls of different shapes sharing one
-// workspace never see another shape's partial sums where they expect zeroed counters.
-constexpr size_t kHeaderBytes = 256;
-constexpr int kMaxTiles = 16384;
-constexpr size_t kCounterBytes = (size_t)kMaxTiles * sizeof(int);
+constexpr size_t kHeaderBytes = kWsStatusBytes;
+constexpr int kMaxTiles = kWsMaxCounters;
+constexpr size_t kCounterBytes = kWsCounterBytes;
 
 }  // namespace
 

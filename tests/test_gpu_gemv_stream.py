@@ -131,3 +131,16 @@ def test_workspace_is_reusable_across_shapes():
     for _ in range(3):
         for blocks, x, first in cases:
             assert np.array_equal(run_linear(blocks, x), first)
+
+
+def test_workspace_is_shared_with_the_batched_kernels():
+    """Batch-1 and batched calls alternate on one workspace without disturbing each other."""
+    blocks, rng = random_blocks(1024, 5120, seed=12)
+    x1 = rng.standard_normal((1, 5120)).astype(np.float16)
+    x8 = rng.standard_normal((8, 5120)).astype(np.float16)
+    x300 = rng.standard_normal((300, 5120)).astype(np.float16)
+    first1, first8 = run_linear(blocks, x1), run_linear(blocks, x8)
+    for _ in range(2):
+        run_linear(blocks, x300)
+        assert np.array_equal(run_linear(blocks, x1), first1)
+        assert np.array_equal(run_linear(blocks, x8), first8)
