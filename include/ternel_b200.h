@@ -107,6 +107,26 @@ size_t tq1_linear_workspace_bytes(int M, int N, int K);
 int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
                    int M, int N, int K, void *workspace, size_t workspace_bytes, void *stream);
 
+/* Batch-1 linear for callers that cannot supply scratch memory. No counterpart in the
+ * reference: it exists for hosts that must not allocate at call time -- code running inside a
+ * stream-capture region (cudaMalloc is illegal there), plugin hosts whose device budget was
+ * fixed when the model was loaded, real-time loops that stay away from the allocator.
+ * Same arithmetic and result as tq1_linear_f16 with M == 1, but the scratch (status word,
+ * arrival counters, per-chunk partial sums) lives in a 2 MiB array built into the library,
+ * which every GPU that loads the library holds until the process exits.
+ *   - Limits: K % 512 == 0, blocks 16-byte aligned, and N*K/128 + 65,792 bytes of scratch must
+ *     fit in 2 MiB (N*K up to about 2.6e8 weights, e.g. 34816 x 5120); larger shapes are
+ *     rejected with TQ1_ERR_WORKSPACE and a message, nothing is launched.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress) with that device current; make that first call outside any
+ *     stream capture.
+ *   - Every call on a device shares the one array and clears its counters on `stream` first,
+ *     so calls that may overlap on the GPU (different streams) race with each other; keep
+ *     them on one stream or order them with events.
+ *   - Calls no cudaMalloc, cudaFree or allocating library routine. */
+int tq1_gemv_f16_noalloc(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
+                         int N, int K, void *stream);
+
 /* out[t][k] = (c[id_t][k]-1) * scale[id_t][k/128], exact; an id outside [0,V)
  * gives a zero row. Replaces tq1_get_rows (src/ternel_mlx/kernels.py:1360-1398,
  * 863-901) and k_get_rows_tq1_g128 (patches/prism-tq1-g128-distribution.patch:132-171).

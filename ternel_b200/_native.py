@@ -32,6 +32,7 @@ SIGNATURES = {
     "tq1_linear_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tq1_linear_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                c_void_p, c_size_t, c_void_p]),
+    "tq1_gemv_f16_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tq1_embedding_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int,
                                   c_void_p]),
 }

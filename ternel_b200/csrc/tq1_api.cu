@@ -38,6 +38,18 @@ int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
     return launch_gemv_rows(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, s);
 }
 
+int tq1_gemv_f16_noalloc(const uint8_t *blocks, const void *x, void *y, int y_is_f32, int N, int K, void *stream) {
+    if (!blocks || !x || !y) return fail(TQ1_ERR_INVALID, "tq1_gemv_f16_noalloc: null pointer");
+    if (N <= 0 || K <= 0)
+        return fail(TQ1_ERR_INVALID, "tensor dimensions must be positive, got %dx%d", N, K);
+    if (K % kGroup)
+        return fail(TQ1_ERR_INVALID, "%d columns is not a multiple of the 128-weight group", K);
+    if (reinterpret_cast<uintptr_t>(x) & 15)
+        return fail(TQ1_ERR_INVALID, "tq1_gemv_f16_noalloc: x must be 16-byte aligned");
+    return gemv_noalloc(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, N, K,
+                        static_cast<cudaStream_t>(stream));
+}
+
 int tq1_embedding_f16(const uint8_t *blocks, const int64_t *ids, void *out, int out_is_f32,
                       int64_t T, int64_t V, int K, void *stream) {
     if (!blocks || !ids || !out) return fail(TQ1_ERR_INVALID, "tq1_embedding_f16: null pointer");

@@ -42,6 +42,8 @@ size_t gemv_stream_workspace_bytes(int N, int K);
 int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K,
                        void *workspace, cudaStream_t stream);
 
+int gemv_noalloc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K, cudaStream_t stream);
+
 // Batched linear (M >= 2) on tcgen05 tensor cores; needs K % 512 == 0 and 16-byte aligned pointers.
 bool gemm_tc_shape_ok(int M, int N, int K);
 bool gemm_tc_supported(const uint8_t *blocks, const __half *x, int M, int N, int K);

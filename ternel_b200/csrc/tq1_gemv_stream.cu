@@ -641,6 +641,51 @@ int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f
     return TQ1_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the batch-1 GEMV.
+//
+// Some hosts cannot give this library scratch memory at call time: code that runs inside a
+// stream-capture region (where cudaMalloc is illegal), plugin hosts whose whole device budget
+// was handed out when the model was loaded, and real-time loops that must not touch the
+// allocator. For them the scratch of the streaming GEMV (status word, arrival counters,
+// per-chunk partial sums) lives in this fixed array, which every GPU that loads the library
+// holds until the process exits.
+constexpr size_t kNoAllocScratchBytes = 2u << 20;       // 2 MiB: N*K up to about 2.6e8 weights
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void *g_noalloc_ptr[kMaxDevices] = {};     // device address of g_noalloc_scratch, per device
+}  // namespace
+
+int gemv_noalloc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K, cudaStream_t stream) {
+    if (!gemv_stream_supported(blocks, N, K))
+        return fail(TQ1_ERR_INVALID,
+                    "tq1_gemv_f16_noalloc: needs K %% 512 == 0, 16-byte aligned blocks and at most %d rows "
+                    "(got N=%d K=%d)", kMaxTiles * kTileRows, N, K);
+    const size_t need = gemv_stream_workspace_bytes(N, K);
+    if (need > kNoAllocScratchBytes)
+        return fail(TQ1_ERR_WORKSPACE,
+                    "tq1_gemv_f16_noalloc: %dx%d needs %zu bytes of scratch, the built-in array holds %zu",
+                    N, K, need, (size_t)kNoAllocScratchBytes);
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return cuda_fail(err, "tq1_gemv_f16_noalloc: cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return fail(TQ1_ERR_INVALID, "tq1_gemv_f16_noalloc: device %d out of range", dev);
+    if (!g_noalloc_ptr[dev]) {
+        // In host code the array's name is only a handle; the kernel needs its device address.
+        void *ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (err != cudaSuccess) return cuda_fail(err, "tq1_gemv_f16_noalloc: cudaGetSymbolAddress");
+        g_noalloc_ptr[dev] = ptr;
+    }
+    unsigned char *scratch = static_cast<unsigned char *>(g_noalloc_ptr[dev]);
+    // The array keeps whatever the last call left: the counters (and the status word) must start at zero.
+    err = cudaMemsetAsync(scratch, 0, kWsScratchOffset, stream);
+    if (err != cudaSuccess) return cuda_fail(err, "tq1_gemv_f16_noalloc: clearing the counters");
+    return launch_gemv_stream(blocks, x, y, y_f32, N, K, scratch, stream);
+}
+
 }  // namespace tq1
 
 #ifdef TQ1_PHASE_TIMERS
