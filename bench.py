@@ -46,6 +46,8 @@ def parse_args():
     p.add_argument("--no-graph", action="store_true", help="launch every kernel from the host each step")
     p.add_argument("--unfused", action="store_true",
                    help="seven launches per layer (q,k,v,o,gate,up,down) instead of four (qkv,o,gate_up,down)")
+    p.add_argument("--exchange", choices=("p2p", "nccl"), default="p2p",
+                   help="how row shards are gathered when --gpus > 1: pushed by the kernels, or NCCL all-gather")
     p.add_argument("--skip-cpu-baseline", action="store_true")
     p.add_argument("--skip-e2e", action="store_true")
     p.add_argument("--skip-batched", action="store_true", help="skip the small-batch and prefill side measurements")
@@ -62,7 +64,9 @@ def workload_config(args) -> dict:
         "launches_per_layer": "7 (q,k,v,o,gate,up,down)" if args.unfused else
                               "4 (q|k|v and gate|up stored row-concatenated: 7168x5120, 5120x5120, 34816x5120, 5120x17408)",
         "packed_weight_bytes": None,   # filled in
-        "parallelism": f"row-sharded x{args.gpus}" if args.gpus > 1 else "single GPU",
+        "parallelism": (f"row-sharded x{args.gpus}, shards exchanged by "
+                        + ("kernel epilogue pushes over NVLink + flags" if args.exchange == "p2p" else "NCCL all-gather")
+                        if args.gpus > 1 else "single GPU"),
         "l2_policy": "inputs larger than L2 (each step streams every layer's distinct weights)",
     }
 
@@ -209,7 +213,7 @@ def run_gpu_arm(args) -> None:
         torch.cuda.synchronize()
 
     stack = LayerStack(layers=args.layers, batch=args.batch, vocab=151936, rank=rank, world=world,
-                       device=device, seed=0, fused=not args.unfused)
+                       device=device, seed=0, fused=not args.unfused, exchange=args.exchange)
     # correctness before timing: one projection of this rank against the C oracle
     if rank == 0:
         from oracle import c_oracle, tq1_oracle as o
@@ -219,7 +223,10 @@ def run_gpu_arm(args) -> None:
         blocks = stack.weights[-1][-1].cpu().numpy()
         x = stack.inputs[k].float().cpu().numpy()
         want = c_oracle.matmul_f32(blocks, x, rows=n // world, columns=k)
-        got = (stack.outputs[n][0] if world > 1 else stack.outputs[n]).float().cpu().numpy().reshape(args.batch, -1)
+        if world > 1 and stack.exchange == "p2p":
+            got = stack.outputs[n][:, : n // world].float().cpu().numpy()
+        else:
+            got = (stack.outputs[n][0] if world > 1 else stack.outputs[n]).float().cpu().numpy().reshape(args.batch, -1)
         err = o.normalised_error(got, want)
         assert err < 2e-3, f"parity check failed before timing: {err}"
 

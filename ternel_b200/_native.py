@@ -32,10 +32,24 @@ SIGNATURES = {
     "tq1_linear_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tq1_linear_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                c_void_p, c_size_t, c_void_p]),
+    "tq1_linear_sharded_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "tq1_shard_advance_epoch": (c_int, [c_void_p, ctypes.c_uint32, c_void_p]),
+    "tq1_linear_f16_sharded": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t,
+                                       c_void_p]),
     "tq1_gemv_f16_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tq1_embedding_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int,
                                   c_void_p]),
 }
+
+class Shard(ctypes.Structure):
+    """Mirror of ``tq1_shard`` in include/ternel_b200.h."""
+    _fields_ = [
+        ("rank", c_int), ("world", c_int), ("n_offset", c_int), ("n_total", c_int),
+        ("peer_y", c_void_p * 8), ("peer_flags", c_void_p * 8),
+        ("epoch_base", c_void_p), ("publish_epoch", ctypes.c_uint32), ("wait_flags", c_void_p),
+        ("wait_epoch", ctypes.c_uint32),
+    ]
+
 
 _lib: ctypes.CDLL | None = None
 

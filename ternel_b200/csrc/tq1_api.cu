@@ -38,6 +38,66 @@ int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
     return launch_gemv_rows(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, s);
 }
 
+static size_t shard_local_bytes(int M, int N_local) {
+    return ((size_t)M * N_local * sizeof(__half) + 255) & ~(size_t)255;
+}
+
+size_t tq1_linear_sharded_workspace_bytes(int M, int N_local, int K) {
+    size_t base = tq1_linear_workspace_bytes(M, N_local, K);
+    if (base < kWsScratchOffset) base = kWsScratchOffset;
+    base = (base + 255) & ~(size_t)255;
+    return base + shard_local_bytes(M, N_local);
+}
+
+int tq1_shard_advance_epoch(uint32_t *epoch_base, uint32_t delta, void *stream) {
+    if (!epoch_base) return fail(TQ1_ERR_INVALID, "tq1_shard_advance_epoch: null pointer");
+    return launch_epoch_advance(epoch_base, delta, static_cast<cudaStream_t>(stream));
+}
+
+int tq1_linear_f16_sharded(const uint8_t *blocks, const void *x, const tq1_shard *shard, int M, int N_local, int K,
+                           void *workspace, size_t workspace_bytes, void *stream) {
+    if (!blocks || !x || !shard) return fail(TQ1_ERR_INVALID, "tq1_linear_f16_sharded: null pointer");
+    if (shard->world < 1 || shard->world > kMaxRanks || shard->rank < 0 || shard->rank >= shard->world)
+        return fail(TQ1_ERR_INVALID, "tq1_linear_f16_sharded: rank %d of %d is out of range (at most %d ranks)",
+                    shard->rank, shard->world, kMaxRanks);
+    if (M <= 0) return fail(TQ1_ERR_INVALID, "activations have an empty batch dimension");
+    if (N_local <= 0 || K <= 0 || K % kGroup)
+        return fail(TQ1_ERR_INVALID, "tq1_linear_f16_sharded: bad shard shape %dx%d", N_local, K);
+    if (shard->n_offset < 0 || shard->n_offset % 16 || shard->n_offset + N_local > shard->n_total)
+        return fail(TQ1_ERR_INVALID, "tq1_linear_f16_sharded: rows [%d, %d) do not fit %d gathered rows "
+                    "(the offset must be a multiple of 16)", shard->n_offset, shard->n_offset + N_local, shard->n_total);
+    const size_t need = tq1_linear_sharded_workspace_bytes(M, N_local, K);
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
+        return fail(TQ1_ERR_WORKSPACE, "tq1_linear_f16_sharded: workspace of %zu bytes (256-byte aligned) required", need);
+    ShardDev sd = {};
+    sd.world = shard->world;
+    sd.rank = shard->rank;
+    for (int p = 0; p < shard->world; ++p) {
+        if (!shard->peer_y[p] || !shard->peer_flags[p])
+            return fail(TQ1_ERR_INVALID, "tq1_linear_f16_sharded: missing peer pointer for rank %d", p);
+        sd.peer_y[p] = static_cast<__half *>(shard->peer_y[p]) + shard->n_offset;
+        sd.peer_flags[p] = shard->peer_flags[p];
+    }
+    sd.epoch_base = shard->epoch_base;
+    sd.publish_epoch = shard->publish_epoch;
+    sd.wait_flags = shard->wait_flags;
+    sd.wait_epoch = shard->wait_epoch;
+    sd.ld_total = shard->n_total;
+    unsigned *status = static_cast<unsigned *>(workspace);
+    sd.done_counter = status + 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (M == 1 && gemv_stream_supported(blocks, N_local, K))     // the GEMV's epilogue does the push itself
+        return launch_gemv_stream(blocks, static_cast<const __half *>(x), nullptr, false, N_local, K, workspace, s, &sd);
+    // general path: wait for the inputs, compute the local slice, push it
+    int rc = launch_shard_wait(sd, status, s);
+    if (rc != TQ1_OK) return rc;
+    const size_t base = need - shard_local_bytes(M, N_local);
+    __half *local = reinterpret_cast<__half *>(static_cast<unsigned char *>(workspace) + base);
+    rc = tq1_linear_f16(blocks, x, local, 0, M, N_local, K, workspace, base, stream);
+    if (rc != TQ1_OK) return rc;
+    return launch_shard_push(local, M, N_local, sd, s);
+}
+
 int tq1_gemv_f16_noalloc(const uint8_t *blocks, const void *x, void *y, int y_is_f32, int N, int K, void *stream) {
     if (!blocks || !x || !y) return fail(TQ1_ERR_INVALID, "tq1_gemv_f16_noalloc: null pointer");
     if (N <= 0 || K <= 0)

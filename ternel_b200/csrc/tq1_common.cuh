@@ -35,12 +35,31 @@ int launch_embedding(const uint8_t *blocks, const int64_t *ids, void *out, bool 
 int launch_gemv_rows(const uint8_t *blocks, const __half *x, void *y, bool y_f32,
                      int M, int N, int K, cudaStream_t stream);
 
+// Device-side description of an output-row shard whose result is pushed to every rank
+// (tq1_linear_f16_sharded): peer pointers are plain device addresses reachable over NVLink.
+constexpr int kMaxRanks = 8;
+struct ShardDev {
+    int world;                          // <= 1: not sharded, every other field is ignored
+    int rank;
+    __half *peer_y[kMaxRanks];          // rank p's gathered output, already advanced to this shard's first row
+    unsigned *peer_flags[kMaxRanks];    // rank p's flag words; word `rank` is ours to write
+    const unsigned *epoch_base;         // optional device word added to both epochs (graph replays advance it)
+    unsigned publish_epoch;             // value published once the whole shard has been written everywhere
+    const unsigned *wait_flags;         // local flag words to wait on before activations are read (or null)
+    unsigned wait_epoch;
+    unsigned *done_counter;             // device word, zero between calls
+    int ld_total;                       // row length of the gathered output (elements)
+};
+
 // Streaming batch-1 GEMV (TMA + integer tensor cores); needs K % 512 == 0 and 16-byte aligned blocks.
 bool gemv_stream_shape_ok(int N, int K);
 bool gemv_stream_supported(const uint8_t *blocks, int N, int K);
 size_t gemv_stream_workspace_bytes(int N, int K);
 int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K,
-                       void *workspace, cudaStream_t stream);
+                       void *workspace, cudaStream_t stream, const ShardDev *shard = nullptr);
+int launch_shard_wait(const ShardDev &shard, unsigned *status, cudaStream_t stream);
+int launch_shard_push(const __half *local, int M, int n_local, const ShardDev &shard, cudaStream_t stream);
+int launch_epoch_advance(unsigned *epoch_base, unsigned delta, cudaStream_t stream);
 
 int gemv_noalloc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K, cudaStream_t stream);
 

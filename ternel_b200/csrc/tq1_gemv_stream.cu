@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *__restrict__ x,
                        void *__restrict__ y, int N, int K, int tiles, int chunks,
                        int *__restrict__ counters, float *__restrict__ partials,
-                       unsigned *__restrict__ status) {
+                       unsigned *__restrict__ status, const ShardDev shard) {
     extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t window = (uint32_t)__cvta_generic_to_shared(smem);   // window address of smem[0]
     // carve-up: [ring | btab | mbarriers | reduction scratch], then the table at a fixed window address
@@ -286,6 +286,20 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     // everything before this kernel has finished before touching activations or the workspace.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (shard.world > 1 && shard.wait_flags != nullptr) {
+        // Row-sharded input: every rank's piece of the activations must have landed in local memory.
+        if (tid < shard.world) {
+            const unsigned want = shard.wait_epoch + (shard.epoch_base ? *shard.epoch_base : 0u);
+            uint32_t spins = 0;
+            for (;;) {
+                unsigned v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(shard.wait_flags + tid) : "memory");
+                if ((int)(v - want) >= 0) break;
+                if (++spins > kMaxWaitSpins) { atomicExch(status, 4u); break; }   // never hang
+            }
+        }
+        __syncthreads();
+    }
     PHASE(1);
 
     // activations of the (at most three) chunks this CTA touches: one thread per activation
@@ -474,6 +488,7 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     __threadfence();
     __syncwarp();
     PHASE(7);
+    int tiles_finished = 0;
     for (int i0 = 0; i0 < n_units; i0 += 32) {
         int last = 0;
         if (i0 + lane < n_units) {
@@ -482,6 +497,7 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
         }
         unsigned todo = __ballot_sync(0xffffffffu, last);
         if (todo) __threadfence();
+        tiles_finished += __popc(todo);
         // This warp completed these row tiles; two are reduced per pass. Lane (ts, jj, rq) adds
         // chunks jj, jj+4, jj+8, ... of rows 4rq..4rq+3 of tile slot ts in ascending order, then a
         // fixed shuffle tree over jj: the order never depends on timing.
@@ -521,13 +537,37 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
                 const int row = tt * kTileRows + 4 * rq;
                 const float out[4] = {total.x, total.y, total.z, total.w};
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    if (row + k < N) {
-                        if (OUT_F32) static_cast<float *>(y)[row + k] = out[k];
-                        else static_cast<__half *>(y)[row + k] = __float2half_rn(out[k]);
+                if (shard.world > 1) {
+                    // fused all-gather: the finished rows go straight into every rank's gathered output
+                    for (int p = 0; p < shard.world; ++p)
+                        for (int k = 0; k < 4; ++k)
+                            if (row + k < N) shard.peer_y[p][row + k] = __float2half_rn(out[k]);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (row + k < N) {
+                            if (OUT_F32) static_cast<float *>(y)[row + k] = out[k];
+                            else static_cast<__half *>(y)[row + k] = __float2half_rn(out[k]);
+                        }
                     }
                 }
                 if (rq == 0) counters[tt] = 0;     // ready for the next call
+            }
+        }
+    }
+    if (shard.world > 1 && tiles_finished > 0) {
+        // Publish: once every row tile of the shard has been written to every rank, raise our flag there.
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+            const unsigned before = atomicAdd(shard.done_counter, (unsigned)tiles_finished);
+            if (before + (unsigned)tiles_finished == (unsigned)tiles) {
+                atomicExch(shard.done_counter, 0u);
+                __threadfence_system();
+                const unsigned epoch = shard.publish_epoch + (shard.epoch_base ? *shard.epoch_base : 0u);
+                for (int p = 0; p < shard.world; ++p)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;"
+                                 ::"l"(shard.peer_flags[p] + shard.rank), "r"(epoch) : "memory");
             }
         }
     }
@@ -574,7 +614,7 @@ size_t gemv_stream_workspace_bytes(int N, int K) {
 }
 
 int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K,
-                       void *workspace, cudaStream_t stream) {
+                       void *workspace, cudaStream_t stream, const ShardDev *shard) {
     EncodeTiledFn encode = encode_fn();
     if (!encode) return fail(TQ1_ERR_CUDA, "tq1_linear_f16: cuTensorMapEncodeTiled is unavailable");
     const int tiles = (N + kTileRows - 1) / kTileRows;
@@ -633,8 +673,14 @@ int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
     const __half *xc = x;
-    cudaError_t err = y_f32 ? cudaLaunchKernelEx(&cfg, kf, map, xc, y, N, K, tiles, chunks, counters, partials, status)
-                            : cudaLaunchKernelEx(&cfg, kh, map, xc, y, N, K, tiles, chunks, counters, partials, status);
+    ShardDev sd = {};
+    if (shard) {
+        sd = *shard;
+        sd.done_counter = status + 1;       // second word of the workspace header, zero between calls
+    }
+    cudaError_t err =
+        y_f32 ? cudaLaunchKernelEx(&cfg, kf, map, xc, y, N, K, tiles, chunks, counters, partials, status, sd)
+              : cudaLaunchKernelEx(&cfg, kh, map, xc, y, N, K, tiles, chunks, counters, partials, status, sd);
     if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: launch");
     err = cudaGetLastError();
     if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: launch");

@@ -83,7 +83,7 @@ class LayerStack:
 
     def __init__(self, *, layers: int, batch: int = 1, shape: LayerShape = LayerShape(),
                  vocab: int = 0, rank: int = 0, world: int = 1, device=None, seed: int = 0,
-                 group=None, fused: bool = False) -> None:
+                 group=None, fused: bool = False, exchange: str = "p2p") -> None:
         self.layers, self.batch, self.shape = layers, batch, shape
         self.rank, self.world, self.group = rank, world, group
         self.device = torch.device(device if device is not None else "cuda")
@@ -116,6 +116,37 @@ class LayerStack:
         self.workspace = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=self.device)
         self.workspace_bytes = ws_bytes
         self.launches_per_step = layers * len(self.projections) + (1 if vocab else 0)
+        self.exchange = exchange if world > 1 else "none"
+        if self.exchange == "p2p":
+            self._setup_peer_buffers()
+
+    def _setup_peer_buffers(self) -> None:
+        """Gathered outputs and flags in symmetric memory so every rank can write into every other's."""
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        from .sharding import EpochClock, ShardPlan
+
+        sizes = sorted({n for _, n, _ in self.projections})
+        self._offsets, cursor = {}, 1024               # [flags 256 B | epoch base 4 B | pad] then the buffers
+        for n in sizes:
+            self._offsets[n] = cursor
+            cursor += (self.batch * n * 2 + 255) // 256 * 256
+        arena = symm_mem.empty(cursor, dtype=torch.uint8, device=self.device)
+        arena.zero_()
+        handle = symm_mem.rendezvous(arena, self.group if self.group is not None else dist.group.WORLD)
+        self._arena, self._handle = arena, handle
+        self._peer_base = [int(p) for p in handle.buffer_ptrs]
+        self.outputs = {n: arena[self._offsets[n]: self._offsets[n] + self.batch * n * 2].view(torch.float16)
+                        .view(self.batch, n) for n in sizes}
+        self._plans = {n: ShardPlan(n, self.world) for n in sizes}
+        self._clock = EpochClock()
+        self._epoch_base_ptr = self._peer_base[self.rank] + 256
+        ws_bytes = max(self.lib.tq1_linear_sharded_workspace_bytes(self.batch, n // self.world, k)
+                       for _, n, k in self.projections)
+        self.workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device=self.device)
+        self.workspace_bytes = ws_bytes
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
 
     # ------------------------------------------------------------------
     @property
@@ -142,6 +173,9 @@ class LayerStack:
         if self.vocab:
             check(lib.tq1_embedding_f16(self.table.data_ptr(), self.ids.data_ptr(), self.embedded.data_ptr(),
                                         0, batch, self.vocab, self.shape.hidden, stream))
+        if self.exchange == "p2p":
+            self._step_p2p(stream)
+            return
         for layer in self.weights:
             for (_, n, k), blocks in zip(self.projections, layer):
                 if world == 1:
@@ -153,6 +187,23 @@ class LayerStack:
                     check(lib.tq1_linear_f16(blocks.data_ptr(), self.inputs[k].data_ptr(), shard.data_ptr(), 0,
                                              batch, n // world, k, ws, ws_bytes, stream))
                     torch.distributed.all_gather_into_tensor(self.outputs[n], shard, group=self.group)
+
+    def _step_p2p(self, stream) -> None:
+        """Every projection pushes its rows into all ranks' gathered buffers; the next one waits for the flags."""
+        from .sharding import make_shard, sharded_linear
+        lib, world, rank = self.lib, self.world, self.rank
+        flags = [base for base in self._peer_base]
+        for layer in self.weights:
+            for (_, n, k), blocks in zip(self.projections, layer):
+                publish, wait = self._clock.next()
+                shard = make_shard(rank=rank, plan=self._plans[n],
+                                   peer_y=[base + self._offsets[n] for base in self._peer_base],
+                                   peer_flags=flags, epoch_base=self._epoch_base_ptr,
+                                   publish_epoch=publish, wait_epoch=wait)
+                sharded_linear(lib, blocks.data_ptr(), self.inputs[k].data_ptr(), shard, batch=self.batch,
+                               n_local=n // world, columns=k, workspace_ptr=self.workspace.data_ptr(),
+                               workspace_bytes=self.workspace_bytes, stream_ptr=stream)
+        check(lib.tq1_shard_advance_epoch(self._epoch_base_ptr, self._clock.reset(), stream))
 
     def checksum(self) -> float:
         """Consumes every output so the work cannot be dead-coded; also a cross-rank equality check."""
