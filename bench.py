@@ -215,10 +215,11 @@ def run_gpu_arm(args) -> None:
     stack = LayerStack(layers=args.layers, batch=args.batch, vocab=151936, rank=rank, world=world,
                        device=device, seed=0, fused=not args.unfused, exchange=args.exchange)
     # correctness before timing: one projection of this rank against the C oracle
+    # (every rank runs the step: sharded steps exchange data and must stay in lockstep)
+    stack.step()
+    barrier()
     if rank == 0:
         from oracle import c_oracle, tq1_oracle as o
-        stack.step()
-        torch.cuda.synchronize()
         name, n, k = stack.projections[-1]     # the last writer of its output buffer
         blocks = stack.weights[-1][-1].cpu().numpy()
         x = stack.inputs[k].float().cpu().numpy()
@@ -282,6 +283,9 @@ def run_gpu_arm(args) -> None:
         e2e = measure_e2e(args, stack, device, world, barrier)
 
     checksum = stack.checksum()
+    status = int(stack.workspace[:4].view(torch.int32)[0].item())
+    if status != 0:
+        raise SystemExit(f"rank {rank}: a bounded device wait ran out (status word {status}); the run is void")
     if rank == 0:
         peaks = {}
         peaks_path = ROOT / "MEASURED_PEAKS.json"
