@@ -6,18 +6,21 @@
 // cuda/tq1_lut23_streamk.cu:113-256, src/ternel_mlx/kernels.py:244-342) behind
 // the same operator; it shares none of their structure.
 //
-// Why integers on the tensor cores. 128 weights arrive per 28 bytes, so at HBM
-// speed an SM has about 1.2 issue slots per weight; one FP32 FMA per weight
-// cannot keep up. Each group's 128 FP16 activations are therefore turned, once
-// per CTA, into 23-bit block fixed point (a shared power-of-two exponent per
-// group, which is as exact as FP32 accumulation) and split into three signed
-// byte planes. The trits (as unsigned codes 0/1/2) are the A operand, the three
-// planes are B columns, and the s32 accumulators hold exact group sums:
-//     sum_k (c_k - 1) x_k = 2^(E-21) * (S0 + 256 S1 + 65536 S2 - sum_k xi_k)
-// followed by acc = fma(scale_g, group_sum, acc) in FP32 as in the reference
-// (src/bonsai_tq1/reference.py:33-38). Groups containing NaN/Inf activations
-// take an FP32 path that multiplies every weight, so non-finite values
-// propagate as in the reference.
+// Why integers on the tensor cores. 128 weights arrive per 28 bytes, so at HBM speed an SM
+// has about 1.2 issue slots per weight; one FP32 FMA per weight cannot keep up. Each group's
+// 128 FP16 activations are therefore turned, once per CTA, into 23-bit block fixed point xi (a
+// shared power-of-two exponent per group, which is as exact as FP32 accumulation). A table
+// lookup turns a code byte b into four signed weights w0..w3 that are used directly as an A
+// register; the fifth trit never has to be extracted, because
+//     b = sum_i 3^i (w_i + 1)   =>   81 * sum_{i<5} w_i x_i
+//                                  = sum_{i<4} w_i (81 x_i - 3^i x_4) + (b - 121) x_4
+// so the raw weight words themselves (four code bytes each) serve as unsigned A registers
+// against x_4, and the other activations enter as 81 x_i - 3^i x_4. Those 30-bit integers are
+// split into four signed byte planes (B columns); the s32 accumulators give 81 * (group sum)
+// modulo 2^32, a multiplication by 81^-1 (mod 2^32) recovers the exact integer group sum, and
+// then acc = fma(scale_g, 2^(E-21) * sum, acc) in FP32 as in the reference
+// (src/bonsai_tq1/reference.py:33-38). Groups containing NaN/Inf activations take an FP32
+// path that multiplies every weight, so non-finite values propagate as in the reference.
 //
 // Work decomposition. A unit is 16 rows x 4 groups (1792 bytes, one TMA box).
 // Units are numbered chunk-major and dealt out in contiguous ranges to the
@@ -29,8 +32,8 @@
 //
 // Lane roles inside mma.m16n8k32 (g = lane/4, q = lane%4): lane (g,q) decodes
 // half a block of row g and half a block of row g+8; q>>1 picks which of the
-// sub-unit's two groups, q&1 which half. B columns 0..2 carry the three digit
-// planes of the first group, columns 4..6 those of the second, and a B lane
+// sub-unit's two groups, q&1 which half. B columns 0..3 carry the four digit
+// planes of the first group, columns 4..7 those of the second, and a B lane
 // holds zeros for k-slots that belong to the other group, which keeps the two
 // groups' sums apart in one instruction.
 #include <cuda.h>
@@ -62,8 +65,10 @@ constexpr uint32_t kRingBytes = kWarps * kStages * kUnitBytes;                  
 constexpr uint32_t kBtabBytes = kMaxChunksPerCta * 2 * kRegsPerSub * 32 * 4;     // 13824
 constexpr uint32_t kMbarBytes = 8 * (kWarps * kStages + 2);                        // per-warp stages + table barrier
 constexpr uint32_t kRedBytes = 3 * 4 * kWarps * kMaxChunksPerCta;                  // group max / sum / non-finite flags
-constexpr uint32_t kCarveBytes = kRingBytes + kBtabBytes + kMbarBytes + kRedBytes;
-static_assert(kCarveBytes + 1024 + 128 <= kLutWindowAddr, "buffers must end below the table's fixed address");
+constexpr uint32_t kXiBytes = 4 * kMaxChunksPerCta * kChunkGroups * kGroup;        // fixed-point activations (exchange)
+constexpr uint32_t kHighBytes = kBtabBytes + kXiBytes + kMbarBytes + kRedBytes;    // region above the table
+static_assert(kRingBytes + 1024 + 128 <= kLutWindowAddr, "the ring must end below the table's fixed address");
+static_assert(kWindowEnd + kHighBytes <= 227 * 1024, "shared memory budget");
 constexpr uint32_t kMaxWaitSpins = 1u << 22;
 
 // Optional phase timers (build with -DTQ1_PHASE_TIMERS): the last warp of every CTA records
@@ -83,41 +88,35 @@ __device__ __forceinline__ void phase_mark(int idx) {
 #define PHASE(i)
 #endif
 
-// The decode table as it sits in shared memory, built at compile time: entry v (a code
-// byte) holds the PRMT selector nibbles of trits c0..c3 in its low half and trit c4 in
-// byte 2 (variant A) or byte 3 (variant B); each variant is replicated for the 32 lanes
-// so that lane i always reads bank i. A CTA fetches the image with one bulk copy.
+// The decode table as it sits in shared memory, built at compile time: entry v (a code byte)
+// holds the weights (trit - 1) of trits 0..3 as four signed bytes, i.e. a ready A register.
+// Entries are 256 bytes apart (so one PRMT can build the address from a code byte) and
+// replicated for the 32 lanes, so lane i always reads bank i. A CTA fetches the image with one
+// bulk copy.
 struct LutImage {
     uint32_t w[243 * 64];
 };
 constexpr LutImage make_lut_image() {
     LutImage img{};
     for (int v = 0; v < 243; ++v) {
-        uint32_t c[5] = {0, 0, 0, 0, 0};
+        uint32_t entry = 0;
         int t = v;
-        for (int d = 0; d < 5; ++d) { c[d] = (uint32_t)(t % 3); t /= 3; }
-        const uint32_t low = c[0] | (c[1] << 4) | (c[2] << 8) | (c[3] << 12);
-        for (int l = 0; l < 32; ++l) {
-            img.w[v * 64 + l] = low | (c[4] << 16);
-            img.w[v * 64 + 32 + l] = low | (c[4] << 24);
+        for (int d = 0; d < 4; ++d) {
+            entry |= (uint32_t)((t % 3 - 1) & 0xff) << (8 * d);
+            t /= 3;
         }
+        for (int l = 0; l < 32; ++l) img.w[v * 64 + l] = entry;
     }
     return img;
 }
 __device__ __align__(128) const LutImage g_lut_image = make_lut_image();
 static_assert(sizeof(LutImage) == kLutBytes, "table image size");
 
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+// byte permute with the selector as an immediate (no register has to hold it)
+template <uint32_t SEL>
+__device__ __forceinline__ uint32_t prmt_imm(uint32_t a, uint32_t b) {
     uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
-
-// a + b issued as an integer multiply-add, which runs on the FMA pipe and leaves the
-// (half-rate) integer ALU to the byte permutes
-__device__ __forceinline__ uint32_t add_fma_pipe(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mad.lo.u32 %0, %1, 1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "n"(SEL));
     return d;
 }
 
@@ -137,12 +136,33 @@ __device__ __forceinline__ uint32_t lds_lut(uint32_t addr) {
     return v;
 }
 
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// D = A * B + C with B signed bytes and A signed (SIGNED_A) or unsigned bytes; ZERO_C starts a chain.
+template <bool SIGNED_A, bool ZERO_C>
+__device__ __forceinline__ void mma_bytes(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    if (ZERO_C) {
+        if (SIGNED_A)
+            asm volatile(
+                "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+        else
+            asm volatile(
+                "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+    } else {
+        if (SIGNED_A)
+            asm volatile(
+                "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+        else
+            asm volatile(
+                "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
 }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -171,36 +191,29 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 
-// Decode one lane-stream (half a block: 14 code-byte slots) into 18 A registers.
-// wa..wd are the four 32-bit words holding the slots (wa: bytes 2,3 only).
+// One lane-stream (half a block: 14 code-byte slots in four words, wa holding slots 0,1 in its
+// upper half) becomes 18 A registers: 14 table entries (weights of trits 0..3 of each slot) and
+// the four raw words (the code bytes themselves, paired with the fifth trit's activation).
 __device__ __forceinline__ void decode_stream(uint32_t wa, uint32_t wb, uint32_t wc, uint32_t wd,
                                               uint32_t lane_base, uint32_t (&r)[kRegsPerSub]) {
-    const uint32_t pool = 0x03020100u;
-    uint32_t e[14];
-    // slot s uses table variant A (c4 in byte 2) when s is even, B (c4 in byte 3) when odd
-    e[0] = lds_lut<0>(prmt(wa, lane_base, 0x7624));
-    e[1] = lds_lut<128>(prmt(wa, lane_base, 0x7634));
-    e[2] = lds_lut<0>(prmt(wb, lane_base, 0x7604));
-    e[3] = lds_lut<128>(prmt(wb, lane_base, 0x7614));
-    e[4] = lds_lut<0>(prmt(wb, lane_base, 0x7624));
-    e[5] = lds_lut<128>(prmt(wb, lane_base, 0x7634));
-    e[6] = lds_lut<0>(prmt(wc, lane_base, 0x7604));
-    e[7] = lds_lut<128>(prmt(wc, lane_base, 0x7614));
-    e[8] = lds_lut<0>(prmt(wc, lane_base, 0x7624));
-    e[9] = lds_lut<128>(prmt(wc, lane_base, 0x7634));
-    e[10] = lds_lut<0>(prmt(wd, lane_base, 0x7604));
-    e[11] = lds_lut<128>(prmt(wd, lane_base, 0x7614));
-    e[12] = lds_lut<0>(prmt(wd, lane_base, 0x7624));
-    e[13] = lds_lut<128>(prmt(wd, lane_base, 0x7634));
-#pragma unroll
-    for (int s = 0; s < 14; ++s) r[s] = prmt(pool, 0u, e[s]);       // nibbles c0..c3 -> four u8 codes
-#pragma unroll
-    for (int u = 0; u < 3; ++u) {
-        const uint32_t x = add_fma_pipe(e[4 * u], e[4 * u + 1]);     // bytes 2,3 = c4 of slots 4u, 4u+1
-        const uint32_t y = add_fma_pipe(e[4 * u + 2], e[4 * u + 3]);
-        r[14 + u] = prmt(x, y, 0x7632);
-    }
-    r[17] = prmt(add_fma_pipe(e[12], e[13]), 0u, 0x4432);
+    r[0] = lds_lut<0>(prmt_imm<0x7624>(wa, lane_base));
+    r[1] = lds_lut<0>(prmt_imm<0x7634>(wa, lane_base));
+    r[2] = lds_lut<0>(prmt_imm<0x7604>(wb, lane_base));
+    r[3] = lds_lut<0>(prmt_imm<0x7614>(wb, lane_base));
+    r[4] = lds_lut<0>(prmt_imm<0x7624>(wb, lane_base));
+    r[5] = lds_lut<0>(prmt_imm<0x7634>(wb, lane_base));
+    r[6] = lds_lut<0>(prmt_imm<0x7604>(wc, lane_base));
+    r[7] = lds_lut<0>(prmt_imm<0x7614>(wc, lane_base));
+    r[8] = lds_lut<0>(prmt_imm<0x7624>(wc, lane_base));
+    r[9] = lds_lut<0>(prmt_imm<0x7634>(wc, lane_base));
+    r[10] = lds_lut<0>(prmt_imm<0x7604>(wd, lane_base));
+    r[11] = lds_lut<0>(prmt_imm<0x7614>(wd, lane_base));
+    r[12] = lds_lut<0>(prmt_imm<0x7624>(wd, lane_base));
+    r[13] = lds_lut<0>(prmt_imm<0x7634>(wd, lane_base));
+    r[14] = wa;
+    r[15] = wb;
+    r[16] = wc;
+    r[17] = wd;
 }
 
 // FP32 fallback for one block (row-major canonical bytes in shared memory) against
@@ -228,14 +241,16 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
                        unsigned *__restrict__ status, const ShardDev shard) {
     extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t window = (uint32_t)__cvta_generic_to_shared(smem);   // window address of smem[0]
-    // carve-up: [ring | btab | mbarriers | reduction scratch], then the table at a fixed window address
+    // carve-up: the ring below the table's fixed window address, everything else above the table
     unsigned char *ring = smem;
-    uint32_t *btab = reinterpret_cast<uint32_t *>(smem + kRingBytes);
-    uint64_t *mbars = reinterpret_cast<uint64_t *>(smem + kRingBytes + kBtabBytes);
-    float *red_max = reinterpret_cast<float *>(smem + kRingBytes + kBtabBytes + kMbarBytes);   // [chunk][warp]
+    unsigned char *high = smem + (kWindowEnd - window);
+    uint32_t *btab = reinterpret_cast<uint32_t *>(high);
+    int *xi_ex = reinterpret_cast<int *>(high + kBtabBytes);                                    // [chunk][512]
+    uint64_t *mbars = reinterpret_cast<uint64_t *>(high + kBtabBytes + kXiBytes);
+    float *red_max = reinterpret_cast<float *>(high + kBtabBytes + kXiBytes + kMbarBytes);     // [chunk][warp]
     int *red_sum = reinterpret_cast<int *>(red_max + kMaxChunksPerCta * kWarps);
     int *red_bad = red_sum + kMaxChunksPerCta * kWarps;
-    if (window + kCarveBytes > kLutWindowAddr) {      // the fixed-address table would overlap the buffers
+    if (window + kRingBytes > kLutWindowAddr) {      // the fixed-address table would overlap the ring
         if (threadIdx.x == 0) atomicExch(status, 2u);
         return;
     }
@@ -312,7 +327,7 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     for (int i = tid; i < (int)(kBtabBytes / 16); i += kThreads)
         reinterpret_cast<uint4 *>(btab)[i] = make_uint4(0u, 0u, 0u, 0u);
 
-    // ---- activation digits: group maximum, fixed point, three signed byte planes ------------------
+    // ---- activation digits: group maximum, fixed point, four signed byte planes ---------------------
     bool bad[kMaxChunksPerCta];
     const int n_chunks_cta = chunk_hi - chunk_lo + 1;
 #pragma unroll
@@ -331,18 +346,14 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     }
     __syncthreads();
     PHASE(2);
+    // where this thread's activation sits in the B fragments (same for every chunk)
+    const int gi = tid >> 7;                           // group within the chunk
+    const int el = tid & 127;
+    const int bj = el < 125 ? el / 5 : 25;             // code byte
+    const int bi = el < 125 ? el - 5 * bj : el - 125;  // trit within the byte
+    const bool is_fifth = el < 125 && bi == 4;         // pairs with the raw code byte
+    int xi[kMaxChunksPerCta];
     {
-        // where this thread's activation sits in the B fragments (same for every chunk)
-        const int gi = tid >> 7;                           // group within the chunk
-        const int el = tid & 127;
-        const int j = el < 125 ? el / 5 : 25;              // code byte
-        const int i = el < 125 ? el - 5 * j : el - 125;    // trit within the byte
-        const int hh = j < 14 ? 0 : 1;                     // which half-block lane decodes it
-        const int slot = hh ? j - 12 : j;
-        const int reg = i < 4 ? slot : 14 + (slot >> 2);
-        const int pos = i < 4 ? i : (slot & 3);
-        const int sub = gi & 1, cg = gi >> 1;
-        const int owner = 4 * (4 * cg) + 2 * cg + hh;      // B lane of digit plane 0; planes 1,2 are +4, +8
         const int gw = warp & ~3;                          // the four warps of this thread's group
 #pragma unroll
         for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
@@ -352,20 +363,45 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
             // 2^E <= m < 2^(E+1); fixed point xi = round(v * 2^(21-E)), |xi| <= 2^22
             const int e_biased = m > 0.0f ? (int)(__float_as_uint(m) >> 23) : 127;
             const float up = __uint_as_float((uint32_t)(275 - e_biased) << 23);            // 2^(21-E)
-            const int xi = bad[cl] ? 0 : __float2int_rn(xv[cl] * up);
-            const int d0 = (xi << 24) >> 24;
-            const int r1 = (xi - d0) >> 8;
-            const int d1 = (r1 << 24) >> 24;
-            const int d2 = (r1 - d1) >> 8;
-            int s = xi;
+            xi[cl] = bad[cl] ? 0 : __float2int_rn(xv[cl] * up);
+            xi_ex[cl * (kChunkGroups * kGroup) + tid] = xi[cl];
+            int s = is_fifth ? 121 * xi[cl] : 0;               // 121 * sum of the fifth-trit activations
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
             if (lane == 0) red_sum[cl * kWarps + warp] = s;
+        }
+    }
+    __syncthreads();
+    {
+        const int hh = bj < 14 ? 0 : 1;                    // which half-block lane decodes it
+        const int slot = hh ? bj - 12 : bj;
+        // trits 0..3 sit in the table-entry register of their slot; a fifth trit pairs with the raw word
+        const int reg = !is_fifth ? slot : slot < 2 ? 14 : 15 + ((slot - 2) >> 2);
+        const int pos = !is_fifth ? bi : slot < 2 ? slot + 2 : ((slot - 2) & 3);
+        const int sub = gi & 1, cg = gi >> 1;
+        const int owner = 4 * (4 * cg) + 2 * cg + hh;      // B lane of digit plane 0; plane p is 4p lanes on
+        const int pow3 = bi == 0 ? 1 : bi == 1 ? 3 : bi == 2 ? 9 : 27;
+#pragma unroll
+        for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
+            if (cl >= n_chunks_cta) break;
+            // value paired with this k-slot: x_4 for the raw byte, 81 x_i - 3^i x_4 for trit i < 4
+            int v = xi[cl];
+            if (!is_fifth) {
+                const int x4 = el < 125 ? xi_ex[cl * (kChunkGroups * kGroup) + gi * kGroup + 5 * bj + 4] : 0;
+                v = 81 * xi[cl] - pow3 * x4;
+            }
+            const int d0 = (v << 24) >> 24;
+            const int r1 = (v - d0) >> 8;
+            const int d1 = (r1 << 24) >> 24;
+            const int r2 = (r1 - d1) >> 8;
+            const int d2 = (r2 << 24) >> 24;
+            const int d3 = (r2 - d2) >> 8;
             unsigned char *base = reinterpret_cast<unsigned char *>(btab) +
                                   ((((cl * 2 + sub) * kRegsPerSub + reg) * 32 + owner) * 4) + pos;
             base[0] = (unsigned char)d0;
             base[16] = (unsigned char)d1;
             base[32] = (unsigned char)d2;
+            base[48] = (unsigned char)d3;
         }
     }
     __syncthreads();
@@ -434,25 +470,34 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
             uint32_t r1[kRegsPerSub], r2[kRegsPerSub];
             decode_stream(w1a, w1b, w1c, w1d, lane_base, r1);
             decode_stream(w2a, w2b, w2c, w2d, lane_base, r2);
-            // three independent accumulator chains keep the tensor pipe's latency off the critical path
-            int accA[4] = {0, 0, 0, 0}, accB[4] = {0, 0, 0, 0}, accC[4] = {0, 0, 0, 0};
-#pragma unroll
-            for (int k = 0; k < kRegsPerSub / 2; k += 3) {
-                mma_u8s8(accA, r1[2 * k], r2[2 * k], r1[2 * k + 1], r2[2 * k + 1], breg[sub][2 * k], breg[sub][2 * k + 1]);
-                mma_u8s8(accB, r1[2 * k + 2], r2[2 * k + 2], r1[2 * k + 3], r2[2 * k + 3], breg[sub][2 * k + 2],
-                         breg[sub][2 * k + 3]);
-                mma_u8s8(accC, r1[2 * k + 4], r2[2 * k + 4], r1[2 * k + 5], r2[2 * k + 5], breg[sub][2 * k + 4],
-                         breg[sub][2 * k + 5]);
-            }
+            // three independent accumulator chains keep the tensor pipe's latency off the critical path;
+            // register pairs 0..6 hold signed weights, pairs 7,8 the raw (unsigned) code bytes
+            int accA[4], accB[4], accC[4];
+            mma_bytes<true, true>(accA, r1[0], r2[0], r1[1], r2[1], breg[sub][0], breg[sub][1]);
+            mma_bytes<true, true>(accB, r1[2], r2[2], r1[3], r2[3], breg[sub][2], breg[sub][3]);
+            mma_bytes<true, true>(accC, r1[4], r2[4], r1[5], r2[5], breg[sub][4], breg[sub][5]);
+            mma_bytes<true, false>(accA, r1[6], r2[6], r1[7], r2[7], breg[sub][6], breg[sub][7]);
+            mma_bytes<true, false>(accB, r1[8], r2[8], r1[9], r2[9], breg[sub][8], breg[sub][9]);
+            mma_bytes<true, false>(accC, r1[10], r2[10], r1[11], r2[11], breg[sub][10], breg[sub][11]);
+            mma_bytes<true, false>(accA, r1[12], r2[12], r1[13], r2[13], breg[sub][12], breg[sub][13]);
+            mma_bytes<false, false>(accB, r1[14], r2[14], r1[15], r2[15], breg[sub][14], breg[sub][15]);
+            mma_bytes<false, false>(accC, r1[16], r2[16], r1[17], r2[17], breg[sub][16], breg[sub][17]);
             int acc[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) acc[k] = accA[k] + accB[k] + accC[k];
-            // columns: lane q=0 holds planes 0,1 of the first group, q=1 plane 2; q=2/3 the second group
-            const int hi1 = __shfl_down_sync(0xffffffffu, acc[0], 1);
-            const int hi2 = __shfl_down_sync(0xffffffffu, acc[2], 1);
+            // columns: lane q=0 holds planes 0,1 of the first group, q=1 planes 2,3; q=2/3 the second group
+            const uint32_t p2r1 = (uint32_t)__shfl_down_sync(0xffffffffu, acc[0], 1);
+            const uint32_t p3r1 = (uint32_t)__shfl_down_sync(0xffffffffu, acc[1], 1);
+            const uint32_t p2r2 = (uint32_t)__shfl_down_sync(0xffffffffu, acc[2], 1);
+            const uint32_t p3r2 = (uint32_t)__shfl_down_sync(0xffffffffu, acc[3], 1);
             if (h == 0) {
-                const int s1 = acc[0] + acc[1] * 256 + hi1 * 65536 - gsum[sub];
-                const int s2 = acc[2] + acc[3] * 256 + hi2 * 65536 - gsum[sub];
+                // 81 * (group sum) modulo 2^32, then times 81^-1 modulo 2^32: the exact integer group sum
+                const uint32_t t1 = (uint32_t)acc[0] + ((uint32_t)acc[1] << 8) + (p2r1 << 16) + (p3r1 << 24) -
+                                    (uint32_t)gsum[sub];
+                const uint32_t t2 = (uint32_t)acc[2] + ((uint32_t)acc[3] << 8) + (p2r2 << 16) + (p3r2 << 24) -
+                                    (uint32_t)gsum[sub];
+                const int s1 = (int)(t1 * 0x781948b1u);
+                const int s2 = (int)(t2 * 0x781948b1u);
                 float dot1 = (float)s1 * gpow[sub];
                 float dot2 = (float)s2 * gpow[sub];
                 if (gbad[sub]) {
@@ -536,7 +581,6 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
             if (bit >= 0 && jj == 0) {
                 const int row = tt * kTileRows + 4 * rq;
                 const float out[4] = {total.x, total.y, total.z, total.w};
-#pragma unroll
                 if (shard.world > 1) {
                     // fused all-gather: the finished rows go straight into every rank's gathered output
                     for (int p = 0; p < shard.world; ++p)
@@ -644,7 +688,7 @@ int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f
         if (sm_count <= 0) sm_count = 148;
     }
     // dynamic shared memory must reach the end of the table whatever the window base is (<= 1 KiB reserved)
-    smem_bytes = kWindowEnd;
+    smem_bytes = kWindowEnd + kHighBytes;
     auto kh = tq1_gemv_stream_kernel<false>;
     auto kf = tq1_gemv_stream_kernel<true>;
     static bool attr_set = false;     // one process drives one GPU
