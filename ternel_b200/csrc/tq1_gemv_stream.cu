@@ -65,7 +65,7 @@ constexpr uint32_t kRingBytes = kWarps * kStages * kUnitBytes;                  
 constexpr uint32_t kBtabBytes = kMaxChunksPerCta * 2 * kRegsPerSub * 32 * 4;     // 13824
 constexpr uint32_t kMbarBytes = 8 * (kWarps * kStages + 2);                        // per-warp stages + table barrier
 constexpr uint32_t kRedBytes = 3 * 4 * kWarps * kMaxChunksPerCta;                  // group max / sum / non-finite flags
-constexpr uint32_t kXiBytes = 4 * kMaxChunksPerCta * kChunkGroups * kGroup;        // fixed-point activations (exchange)
+constexpr uint32_t kXiBytes = 0;
 constexpr uint32_t kHighBytes = kBtabBytes + kXiBytes + kMbarBytes + kRedBytes;    // region above the table
 static_assert(kRingBytes + 1024 + 128 <= kLutWindowAddr, "the ring must end below the table's fixed address");
 static_assert(kWindowEnd + kHighBytes <= 227 * 1024, "shared memory budget");
@@ -245,7 +245,6 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     unsigned char *ring = smem;
     unsigned char *high = smem + (kWindowEnd - window);
     uint32_t *btab = reinterpret_cast<uint32_t *>(high);
-    int *xi_ex = reinterpret_cast<int *>(high + kBtabBytes);                                    // [chunk][512]
     uint64_t *mbars = reinterpret_cast<uint64_t *>(high + kBtabBytes + kXiBytes);
     float *red_max = reinterpret_cast<float *>(high + kBtabBytes + kXiBytes + kMbarBytes);     // [chunk][warp]
     int *red_sum = reinterpret_cast<int *>(red_max + kMaxChunksPerCta * kWarps);
@@ -260,10 +259,12 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     const int warp = tid >> 5;
 
     PHASE(0);
+    if (tid == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
     // ---- unit range of this CTA and of this warp (units are numbered chunk-major) ----------------
     const int total_units = tiles * chunks;
-    const int cta_begin = (int)((long long)total_units * blockIdx.x / gridDim.x);
-    const int cta_end = (int)((long long)total_units * (blockIdx.x + 1) / gridDim.x);
+    // total_units <= 16384 * 256 and gridDim.x <= a few hundred, so the products fit 32 bits
+    const int cta_begin = (int)((unsigned)total_units * blockIdx.x / gridDim.x);
+    const int cta_end = (int)((unsigned)total_units * (blockIdx.x + 1) / gridDim.x);
     const int cta_units = cta_end - cta_begin;
     const int u_begin = cta_begin + ((cta_units * warp) >> 4);
     const int u_end = cta_begin + ((cta_units * (warp + 1)) >> 4);
@@ -273,7 +274,7 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     const int c_first = u_begin / tiles;
     const int t_first = u_begin - c_first * tiles;
 
-    // ---- first of all, get this warp's weight bytes (and the decode table) moving -----------------
+    // ---- barriers and the decode table first (nothing here depends on the previous kernel) ---------
     const uint32_t ring_warp = window + (uint32_t)(warp * kStages * kUnitBytes);
     const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&mbars[warp * kStages]);
     const uint32_t lut_bar = (uint32_t)__cvta_generic_to_shared(&mbars[kWarps * kStages]);
@@ -295,7 +296,6 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
             mbar_expect_tx(lut_bar, kLutBytes);
             bulk_load(kLutWindowAddr, &g_lut_image, kLutBytes, lut_bar);
         }
-        while (issued < kStages - 1 && issued < n_units) issue_next();
     }
     // Let the next kernel in the stream start its own prologue as SMs free up, then wait until
     // everything before this kernel has finished before touching activations or the workspace.
@@ -317,13 +317,26 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     }
     PHASE(1);
 
-    // activations of the (at most three) chunks this CTA touches: one thread per activation
-    float xv[kMaxChunksPerCta];
+    // activations of the (at most three) chunks this CTA touches: one thread per activation, which
+    // also fetches the activation of the fifth trit of its code byte (needed for 81 x_i - 3^i x_4)
+    const int gi = tid >> 7;                           // group within the chunk
+    const int el = tid & 127;
+    const int bj = el < 125 ? el / 5 : 25;             // code byte
+    const int bi = el < 125 ? el - 5 * bj : el - 125;  // trit within the byte
+    const bool is_fifth = el < 125 && bi == 4;         // pairs with the raw code byte
+    const int fifth = el < 125 ? gi * kGroup + 5 * bj + 4 : tid;
+    float xv[kMaxChunksPerCta], x4v[kMaxChunksPerCta];
 #pragma unroll
-    for (int cl = 0; cl < kMaxChunksPerCta; ++cl)
-        xv[cl] = chunk_lo + cl <= chunk_hi
-                     ? __half2float(__ldg(x + (size_t)(chunk_lo + cl) * (kChunkGroups * kGroup) + tid))
-                     : 0.0f;
+    for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
+        const bool live = chunk_lo + cl <= chunk_hi;
+        const __half *xc = x + (size_t)(chunk_lo + cl) * (kChunkGroups * kGroup);
+        xv[cl] = live ? __half2float(__ldg(xc + tid)) : 0.0f;
+        x4v[cl] = live ? __half2float(__ldg(xc + fifth)) : 0.0f;
+    }
+    // The activation loads are in flight: now start this warp's weight tiles. (Issued the other way
+    // round, the few activation bytes queue behind megabytes of weight traffic and arrive 1-2 us late.)
+    if (lane == 0)
+        while (issued < kStages - 1 && issued < n_units) issue_next();
     for (int i = tid; i < (int)(kBtabBytes / 16); i += kThreads)
         reinterpret_cast<uint4 *>(btab)[i] = make_uint4(0u, 0u, 0u, 0u);
 
@@ -346,32 +359,6 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     }
     __syncthreads();
     PHASE(2);
-    // where this thread's activation sits in the B fragments (same for every chunk)
-    const int gi = tid >> 7;                           // group within the chunk
-    const int el = tid & 127;
-    const int bj = el < 125 ? el / 5 : 25;             // code byte
-    const int bi = el < 125 ? el - 5 * bj : el - 125;  // trit within the byte
-    const bool is_fifth = el < 125 && bi == 4;         // pairs with the raw code byte
-    int xi[kMaxChunksPerCta];
-    {
-        const int gw = warp & ~3;                          // the four warps of this thread's group
-#pragma unroll
-        for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
-            if (cl >= n_chunks_cta) break;
-            const float *rm = red_max + cl * kWarps + gw;
-            const float m = fmaxf(fmaxf(rm[0], rm[1]), fmaxf(rm[2], rm[3]));
-            // 2^E <= m < 2^(E+1); fixed point xi = round(v * 2^(21-E)), |xi| <= 2^22
-            const int e_biased = m > 0.0f ? (int)(__float_as_uint(m) >> 23) : 127;
-            const float up = __uint_as_float((uint32_t)(275 - e_biased) << 23);            // 2^(21-E)
-            xi[cl] = bad[cl] ? 0 : __float2int_rn(xv[cl] * up);
-            xi_ex[cl * (kChunkGroups * kGroup) + tid] = xi[cl];
-            int s = is_fifth ? 121 * xi[cl] : 0;               // 121 * sum of the fifth-trit activations
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (lane == 0) red_sum[cl * kWarps + warp] = s;
-        }
-    }
-    __syncthreads();
     {
         const int hh = bj < 14 ? 0 : 1;                    // which half-block lane decodes it
         const int slot = hh ? bj - 12 : bj;
@@ -381,14 +368,26 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
         const int sub = gi & 1, cg = gi >> 1;
         const int owner = 4 * (4 * cg) + 2 * cg + hh;      // B lane of digit plane 0; plane p is 4p lanes on
         const int pow3 = bi == 0 ? 1 : bi == 1 ? 3 : bi == 2 ? 9 : 27;
+        const int gw = warp & ~3;                          // the four warps of this thread's group
 #pragma unroll
         for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
             if (cl >= n_chunks_cta) break;
+            const float *rm = red_max + cl * kWarps + gw;
+            const float m = fmaxf(fmaxf(rm[0], rm[1]), fmaxf(rm[2], rm[3]));
+            // 2^E <= m < 2^(E+1); fixed point xi = round(v * 2^(21-E)), |xi| <= 2^22
+            const int e_biased = m > 0.0f ? (int)(__float_as_uint(m) >> 23) : 127;
+            const float up = __uint_as_float((uint32_t)(275 - e_biased) << 23);            // 2^(21-E)
+            const int xi = bad[cl] ? 0 : __float2int_rn(xv[cl] * up);
+            int s = is_fifth ? 121 * xi : 0;                   // 121 * sum of the fifth-trit activations
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0) red_sum[cl * kWarps + warp] = s;
             // value paired with this k-slot: x_4 for the raw byte, 81 x_i - 3^i x_4 for trit i < 4
-            int v = xi[cl];
+            int v = xi;
             if (!is_fifth) {
-                const int x4 = el < 125 ? xi_ex[cl * (kChunkGroups * kGroup) + gi * kGroup + 5 * bj + 4] : 0;
-                v = 81 * xi[cl] - pow3 * x4;
+                const float a4 = fabsf(x4v[cl]);
+                const int x4 = (el < 125 && a4 <= 65504.0f) ? __float2int_rn(x4v[cl] * up) : 0;
+                v = 81 * xi - pow3 * x4;
             }
             const int d0 = (v << 24) >> 24;
             const int r1 = (v - d0) >> 8;
@@ -530,23 +529,38 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
 
     PHASE(6);
     // ---- publish: one fence for all of this warp's partial sums, then one arrival per row tile -----
+    // Row tile t is finished by a fixed owner, the warp that processed its chunk t % chunks: the
+    // owner waits (bounded) until all chunks have arrived. Leaving the reduction to whichever warp
+    // arrives last piles that work onto the slowest CTAs; with fixed owners every warp finishes
+    // about one tile per `chunks` units. All CTAs of the grid are resident (one per SM), so the
+    // owner's wait is for warps that are running.
     __threadfence();
     __syncwarp();
     PHASE(7);
     int tiles_finished = 0;
     for (int i0 = 0; i0 < n_units; i0 += 32) {
-        int last = 0;
+        int mine = 0;
         if (i0 + lane < n_units) {
-            const int tt = (u_begin + i0 + lane) % tiles;
-            last = atomicAdd(&counters[tt], 1) == chunks - 1;
+            const int u = u_begin + i0 + lane;
+            const int cc = u / tiles, tt = u - cc * tiles;
+            atomicAdd(&counters[tt], 1);
+            mine = (tt % chunks) == cc;
         }
-        unsigned todo = __ballot_sync(0xffffffffu, last);
-        if (todo) __threadfence();
+        unsigned todo = __ballot_sync(0xffffffffu, mine);
         tiles_finished += __popc(todo);
-        // This warp completed these row tiles; two are reduced per pass. Lane (ts, jj, rq) adds
-        // chunks jj, jj+4, jj+8, ... of rows 4rq..4rq+3 of tile slot ts in ascending order, then a
-        // fixed shuffle tree over jj: the order never depends on timing.
-        const int ts = lane >> 4, jj = (lane >> 2) & 3, rq = lane & 3;
+        if (mine) {                 // wait for the other chunks of my tiles
+            const int tt = (u_begin + i0 + lane) % tiles;
+            uint32_t spins = 0;
+            while (__ldcg(&counters[tt]) != chunks) {
+                if (++spins > kMaxWaitSpins) { atomicExch(status, 5u); break; }
+            }
+        }
+        __syncwarp();
+        if (todo) __threadfence();
+        // Finish my tiles, two per pass. Lane (ts, cj, rq) adds chunks cj, cj+4, cj+8, ... of rows
+        // 4rq..4rq+3 of tile slot ts in ascending order (all loads of a batch issued before the first
+        // add), then a fixed shuffle tree combines the four chunk lanes: the order never depends on timing.
+        const int ts = lane >> 4, cj = (lane >> 2) & 3, rq = lane & 3;
         const size_t stride = (size_t)tiles * kTileRows;
         while (todo) {
             const int b0 = __ffs(todo) - 1;
@@ -558,16 +572,18 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
             float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             if (bit >= 0) {
                 const float *p = partials + (size_t)tt * kTileRows + 4 * rq;
-                for (int cc = jj; cc < chunks; cc += 32) {
-                    float4 v[8];
+                for (int cc = cj; cc < chunks; cc += 48) {
+                    float4 v[12];
 #pragma unroll
-                    for (int k = 0; k < 8; ++k)
+                    for (int k = 0; k < 12; ++k)
                         v[k] = cc + 4 * k < chunks
                                    ? __ldcg(reinterpret_cast<const float4 *>(p + (size_t)(cc + 4 * k) * stride))
                                    : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        total.x += v[k].x; total.y += v[k].y; total.z += v[k].z; total.w += v[k].w;
+                    for (int k = 0; k < 12; ++k) {
+                        if (cc + 4 * k < chunks) {
+                            total.x += v[k].x; total.y += v[k].y; total.z += v[k].z; total.w += v[k].w;
+                        }
                     }
                 }
             }
@@ -578,14 +594,14 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
                 total.z += __shfl_xor_sync(0xffffffffu, total.z, o);
                 total.w += __shfl_xor_sync(0xffffffffu, total.w, o);
             }
-            if (bit >= 0 && jj == 0) {
+            if (bit >= 0 && cj == 0) {
                 const int row = tt * kTileRows + 4 * rq;
                 const float out[4] = {total.x, total.y, total.z, total.w};
                 if (shard.world > 1) {
                     // fused all-gather: the finished rows go straight into every rank's gathered output
-                    for (int p = 0; p < shard.world; ++p)
+                    for (int p2 = 0; p2 < shard.world; ++p2)
                         for (int k = 0; k < 4; ++k)
-                            if (row + k < N) shard.peer_y[p][row + k] = __float2half_rn(out[k]);
+                            if (row + k < N) shard.peer_y[p2][row + k] = __float2half_rn(out[k]);
                 } else {
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
