@@ -38,8 +38,8 @@ UNIT = "GB/s"
 def parse_args():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=20)
-    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--steps", type=int, default=50)
+    p.add_argument("--warmup", type=int, default=20)
     p.add_argument("--impl", choices=("ours", "reference"), default="ours")
     p.add_argument("--layers", type=int, default=64)
     p.add_argument("--batch", type=int, default=1)
@@ -250,12 +250,12 @@ def run_gpu_arm(args) -> None:
         else:
             stack.step()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()             # nvidia-smi needs a moment to start: sample from the warm-up on
     for _ in range(max(args.warmup, 3)):
         one_step()
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     start.record()
@@ -408,13 +408,21 @@ def measure_batched(device, replays: int = 3):
                     check(lib.tq1_linear_f16(w.data_ptr(), x.data_ptr(), y.data_ptr(), 0, m, n, k,
                                              ws.data_ptr(), ws_bytes, stream))
 
-            for _ in range(2):
+            side = torch.cuda.Stream(device=device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
                 run()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()        # device time, not the host's launch rate
+            with torch.cuda.graph(graph):
+                run()
+            graph.replay()
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             start.record()
             for _ in range(replays):
-                run()
+                graph.replay()
             stop.record()
             torch.cuda.synchronize()
             us = start.elapsed_time(stop) * 1e3 / (replays * len(ring))
@@ -424,7 +432,7 @@ def measure_batched(device, replays: int = 3):
             else:
                 tf = 2.0 * m * n * k / us / 1e6
                 out["prefill"][f"M{m}_{n}x{k}"] = {"us": us, "tflops": tf, "frac_of_measured_peak": tf / peak_tf}
-            del x, y, ws
+            del graph, x, y, ws
         del ring
     return out
 
@@ -442,9 +450,11 @@ def measure_e2e(args, stack, device, world, barrier):
     h2d = sum(v.numel() * 2 for v in host_x.values()) + host_ids.numel() * 8
     d2h = sum(buf.numel() * 2 for _, buf in last)
 
-    def step():
-        dev_x = {k: v.to(device, non_blocking=True) for k, v in host_x.items()}
-        ids = host_ids.to(device, non_blocking=True)
+    keys = sorted(host_x)
+
+    def forward(ids, *xs):
+        """The decode step through the public modules' kernels, device tensors in and out."""
+        dev_x = dict(zip(keys, xs))
         tq1_get_rows(stack.table, ids)
         outs = {}
         for layer in stack.weights:
@@ -455,12 +465,25 @@ def measure_e2e(args, stack, device, world, barrier):
                     dist.all_gather_into_tensor(full, y, group=stack.group)
                     y = full.permute(1, 0, 2).reshape(args.batch, n)
                 outs[n] = y
-        for n, buf in last:
-            buf.copy_(outs[n], non_blocking=True)
+        return tuple(outs[n] for n, _ in last)
+
+    graphed = None
+    if world == 1 and not args.no_graph:
+        from ternel_b200.graphs import GraphedStep
+        graphed = GraphedStep(forward, [stack.ids] + [stack.inputs[k] for k in keys])
+
+    def step():
+        if graphed is not None:         # host -> static device inputs, one graph replay, device -> host
+            outs = graphed(host_ids, *[host_x[k] for k in keys])
+        else:
+            outs = forward(host_ids.to(device, non_blocking=True),
+                           *[host_x[k].to(device, non_blocking=True) for k in keys])
+        for (n, buf), y in zip(last, outs):
+            buf.copy_(y, non_blocking=True)
         torch.cuda.synchronize()
 
-    steps = max(3, min(args.steps, 10))
-    for _ in range(2):
+    steps = max(3, min(args.steps, 20))
+    for _ in range(3):
         step()
     barrier()
     t0 = time.perf_counter()
@@ -474,7 +497,9 @@ def measure_e2e(args, stack, device, world, barrier):
     sec = float(t.item())
     return {"value": stack.algorithmic_bytes_per_step * world / sec / 1e9, "unit": UNIT,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": sec * 1e3,
-            "steps": steps, "api": "torch.ops.ternel.tq1_linear / tq1_embedding, one call per projection"}
+            "steps": steps,
+            "api": "torch.ops.ternel.tq1_linear / tq1_embedding, one call per projection"
+                   + (", captured once by ternel_b200.graphs.GraphedStep and replayed" if graphed is not None else "")}
 
 
 def main():

@@ -8,9 +8,10 @@
 //
 // One CTA computes a tile of 128 weight rows x NT activation rows over a range of K:
 //   D[n][m] = sum_k W[n][k] * x[m][k]      (A = W tile, B = x tile, both K-major FP16)
-//   warps 0-3  decode: thread r turns row r's 28-byte block into 128 FP16 values and writes
-//              them into the 128-byte-swizzled A tile; after the K loop the same warps read
-//              the accumulator (TMEM lane r = weight row r) and store y
+//   warps 0-3, 6-9  decode: thread r of a group turns row r's 28-byte block into 128 FP16 values
+//              and writes them into the 128-byte-swizzled A tile; the two groups take alternate
+//              K blocks. After the K loop warps 0-3 read the accumulator (TMEM lane r = weight
+//              row r) and store y
 //   warp 4     TMA: packed weight bytes (box 128 rows x 112 B = 4 groups) and activation tiles
 //   warp 5     allocates tensor memory and issues tcgen05.mma (one elected lane)
 //
@@ -35,12 +36,15 @@ namespace tq1 {
 namespace {
 
 constexpr int kTileW = 128;                 // weight rows per tile (UMMA M)
-constexpr int kStagesG = 2;
 constexpr int kPackGroups = 4;
 constexpr int kPackBytes = kTileW * kPackGroups * kBlockBytes;     // 14336
 constexpr int kATileBytes = kTileW * kGroup * 2;                   // 32768: two 64-wide swizzle atoms
 constexpr int kLutBytesG = 243 * 256;                              // 8-byte entries x 32 lanes
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;            // 2 x 4 decode warps, one TMA warp, one MMA warp
+__host__ __device__ constexpr int gemm_stages(int nt) { return 2; }
+// packed-byte buffers (4 K blocks each): small activation tiles leave room for a deep prefetch queue,
+// which is what hides HBM latency when the tensor work per K block is tiny
+__host__ __device__ constexpr int gemm_pack_bufs(int nt) { return nt <= 32 ? 6 : 2; }
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 __host__ __device__ constexpr int perm_column(int p) {
@@ -162,6 +166,8 @@ template <int NT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                    const GemmParams prm) {
+    constexpr int kStagesG = gemm_stages(NT);
+    constexpr int kPackBufs = gemm_pack_bufs(NT);
     constexpr int kBTileBytes = NT * kGroup * 2;
     constexpr int kTmemCols = NT < 32 ? 32 : NT;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -170,11 +176,12 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     unsigned char *a_tiles = smem;                                       // kStagesG x 32 KiB, 1024-aligned
     unsigned char *b_tiles = a_tiles + kStagesG * kATileBytes;           // kStagesG x NT*256
     unsigned char *packed = b_tiles + kStagesG * kBTileBytes;            // 2 x 14336
-    unsigned char *lut = packed + 2 * kPackBytes;                        // 62208
+    unsigned char *lut = packed + kPackBufs * kPackBytes;                // 62208
     uint64_t *bars = reinterpret_cast<uint64_t *>(lut + kLutBytesG);
     // barrier indices
-    enum { FULL_A = 0, FULL_B = FULL_A + kStagesG, EMPTY = FULL_B + kStagesG, PACK_FULL = EMPTY + kStagesG,
-           PACK_EMPTY = PACK_FULL + 2, ACCUM = PACK_EMPTY + 2, LUT_BAR = ACCUM + 1, NUM_BARS = LUT_BAR + 1 };
+    constexpr int FULL_A = 0, FULL_B = FULL_A + kStagesG, EMPTY = FULL_B + kStagesG, PACK_FULL = EMPTY + kStagesG,
+                  PACK_EMPTY = PACK_FULL + kPackBufs, ACCUM = PACK_EMPTY + kPackBufs, LUT_BAR = ACCUM + 1,
+                  NUM_BARS = LUT_BAR + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NUM_BARS);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -194,9 +201,9 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             mbar_init(bar(FULL_B + s), 1);
             mbar_init(bar(EMPTY + s), 1);
         }
-        for (int p = 0; p < 2; ++p) {
+        for (int p = 0; p < kPackBufs; ++p) {
             mbar_init(bar(PACK_FULL + p), 1);
-            mbar_init(bar(PACK_EMPTY + p), 128);
+            mbar_init(bar(PACK_EMPTY + p), 256);
         }
         mbar_init(bar(ACCUM), 1);
         mbar_init(bar(LUT_BAR), 1);
@@ -217,20 +224,22 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
 
     bool ok = true;
     if (warp == 4) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            int pack_i = 0;
+        // ------------------------------------------------------------------ TMA producers
+        // lane 1 keeps the queue of packed-byte chunks full, lane 0 feeds the activation tiles;
+        // the two run independently so that the weight prefetch can run several chunks ahead
+        if (lane == 1) {
+            const int first_chunk = kb_begin / kPackGroups, last_chunk = (kb_end - 1) / kPackGroups;
+            for (int c = first_chunk, pack_i = 0; c <= last_chunk && ok; ++c, ++pack_i) {
+                const int p = pack_i % kPackBufs;
+                ok = mbar_wait(bar(PACK_EMPTY + p), ((uint32_t)(pack_i / kPackBufs) & 1u) ^ 1u, prm.status);
+                if (!ok) break;
+                mbar_expect_tx(bar(PACK_FULL + p), kPackBytes);
+                tma_load_2d((uint32_t)__cvta_generic_to_shared(packed + p * kPackBytes), &wmap,
+                            c * (kPackGroups * kBlockBytes), n0, bar(PACK_FULL + p));
+            }
+        } else if (lane == 0) {
             for (int i = 0; i < n_kb && ok; ++i) {
                 const int kb = kb_begin + i;
-                if (i == 0 || (kb % kPackGroups) == 0) {        // a new 4-group chunk of packed bytes
-                    const int p = pack_i & 1;
-                    ok = mbar_wait(bar(PACK_EMPTY + p), ((uint32_t)(pack_i >> 1) & 1u) ^ 1u, prm.status);
-                    if (!ok) break;
-                    mbar_expect_tx(bar(PACK_FULL + p), kPackBytes);
-                    tma_load_2d((uint32_t)__cvta_generic_to_shared(packed + p * kPackBytes), &wmap,
-                                (kb / kPackGroups) * (kPackGroups * kBlockBytes), n0, bar(PACK_FULL + p));
-                    ++pack_i;
-                }
                 const int s = i % kStagesG;
                 ok = mbar_wait(bar(EMPTY + s), ((uint32_t)(i / kStagesG) & 1u) ^ 1u, prm.status);
                 if (!ok) break;
@@ -268,7 +277,9 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         }
     } else {
         // ------------------------------------------------------------------ decode (thread = weight row)
-        const int r = tid;                               // 0..127
+        // two groups of four warps take alternate K blocks, so two stages are being filled at a time
+        const int group = warp < 4 ? 0 : 1;
+        const int r = warp < 4 ? tid : tid - 192;        // 0..127
         ok = mbar_wait(bar(LUT_BAR), 0, prm.status);
         const uint32_t lut_lane = (uint32_t)__cvta_generic_to_shared(lut) + (uint32_t)lane * 8u;
         const uint32_t row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
@@ -278,15 +289,20 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             const int kb = kb_begin + i;
             if (i == 0 || (kb % kPackGroups) == 0) {
                 ++pack_i;
-                ok = mbar_wait(bar(PACK_FULL + (pack_i & 1)), (uint32_t)(pack_i >> 1) & 1u, prm.status);
+                ok = mbar_wait(bar(PACK_FULL + pack_i % kPackBufs), (uint32_t)(pack_i / kPackBufs) & 1u, prm.status);
                 if (!ok) break;
+            }
+            const bool last_of_chunk = (kb % kPackGroups) == kPackGroups - 1 || i == n_kb - 1;
+            if ((i & 1) != group) {                      // the other group's K block
+                if (last_of_chunk) mbar_arrive(bar(PACK_EMPTY + pack_i % kPackBufs));
+                continue;
             }
             const int s = i % kStagesG;
             ok = mbar_wait(bar(EMPTY + s), ((uint32_t)(i / kStagesG) & 1u) ^ 1u, prm.status);
             if (!ok) break;
 
             const uint32_t *blk = reinterpret_cast<const uint32_t *>(
-                packed + (pack_i & 1) * kPackBytes + (r * kPackGroups + (kb % kPackGroups)) * kBlockBytes);
+                packed + (pack_i % kPackBufs) * kPackBytes + (r * kPackGroups + (kb % kPackGroups)) * kBlockBytes);
             uint32_t w[7];
 #pragma unroll
             for (int k = 0; k < 7; ++k) w[k] = blk[k];
@@ -320,12 +336,12 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             store_chunk(15, c4pair(17, 18), c4pair(19, 20), c4pair(21, 22), c4pair(23, 24));
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
             mbar_arrive(bar(FULL_A + s));
-            if ((kb % kPackGroups) == kPackGroups - 1 || i == n_kb - 1) mbar_arrive(bar(PACK_EMPTY + (pack_i & 1)));
+            if (last_of_chunk) mbar_arrive(bar(PACK_EMPTY + pack_i % kPackBufs));
         }
 
         // ------------------------------------------------------------------ epilogue (TMEM lane = weight row)
-        if (ok) ok = mbar_wait(bar(ACCUM), 0, prm.status);
-        if (ok) {
+        if (ok && group == 0) ok = mbar_wait(bar(ACCUM), 0, prm.status);
+        if (ok && group == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int n = n0 + r;
 #pragma unroll 1
@@ -417,7 +433,8 @@ size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 template <int NT>
 size_t gemm_smem_bytes() {
-    return (size_t)kStagesG * kATileBytes + (size_t)kStagesG * NT * kGroup * 2 + 2 * kPackBytes + kLutBytesG + 256 + 1024;
+    return (size_t)gemm_stages(NT) * kATileBytes + (size_t)gemm_stages(NT) * NT * kGroup * 2 +
+           (size_t)gemm_pack_bufs(NT) * kPackBytes + kLutBytesG + 512 + 1024;
 }
 
 template <int NT>
