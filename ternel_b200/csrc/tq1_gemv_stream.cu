@@ -528,14 +528,13 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     }
 
     PHASE(6);
-    // ---- publish: one fence for all of this warp's partial sums, then one arrival per row tile -----
+    // ---- publish: one release arrival per row tile --------------------------------------------------
     // Row tile t is finished by a fixed owner, the warp that processed its chunk t % chunks: the
     // owner waits (bounded) until all chunks have arrived. Leaving the reduction to whichever warp
     // arrives last piles that work onto the slowest CTAs; with fixed owners every warp finishes
     // about one tile per `chunks` units. All CTAs of the grid are resident (one per SM), so the
     // owner's wait is for warps that are running.
-    __threadfence();
-    __syncwarp();
+    __syncwarp();               // orders the partial-sum stores of all lanes before the releases below
     PHASE(7);
     int tiles_finished = 0;
     for (int i0 = 0; i0 < n_units; i0 += 32) {
@@ -543,7 +542,8 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
         if (i0 + lane < n_units) {
             const int u = u_begin + i0 + lane;
             const int cc = u / tiles, tt = u - cc * tiles;
-            atomicAdd(&counters[tt], 1);
+            // arrival: a release reduction (no return value, so nobody waits for the round trip)
+            asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(counters + tt) : "memory");
             mine = (tt % chunks) == cc;
         }
         unsigned todo = __ballot_sync(0xffffffffu, mine);
@@ -551,12 +551,14 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
         if (mine) {                 // wait for the other chunks of my tiles
             const int tt = (u_begin + i0 + lane) % tiles;
             uint32_t spins = 0;
-            while (__ldcg(&counters[tt]) != chunks) {
+            for (;;) {
+                int v;
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counters + tt) : "memory");
+                if (v == chunks) break;
                 if (++spins > kMaxWaitSpins) { atomicExch(status, 5u); break; }
             }
         }
-        __syncwarp();
-        if (todo) __threadfence();
+        __syncwarp();               // the other lanes' loads below come after the acquiring lanes' loads
         // Finish my tiles, two per pass. Lane (ts, cj, rq) adds chunks cj, cj+4, cj+8, ... of rows
         // 4rq..4rq+3 of tile slot ts in ascending order (all loads of a batch issued before the first
         // add), then a fixed shuffle tree combines the four chunk lanes: the order never depends on timing.
