@@ -1,5 +1,6 @@
 // Batched linear (M >= 2 activation rows) for TQ1_G128 on sm_100a: trits are decoded into
-// FP16 shared-memory tiles that feed tcgen05.mma with FP32 accumulators in tensor memory.
+// FP16 tiles in tensor memory (weights) and shared memory (activations) that feed tcgen05.mma with
+// FP32 accumulators in tensor memory.
 //
 // Stands in for the reference's prefill GEMM and small-batch kernels behind packed_matmul
 // (src/ternel_mlx/kernels.py:409-858,1287-1357; src/ternel_mlx/modules.py:425-457). As in
@@ -8,10 +9,11 @@
 //
 // One CTA computes a tile of 128 weight rows x NT activation rows over a range of K:
 //   D[n][m] = sum_k W[n][k] * x[m][k]      (A = W tile, B = x tile, both K-major FP16)
-//   warps 0-3, 6-9  decode: thread r of a group turns row r's 28-byte block into 128 FP16 values
-//              and writes them into the 128-byte-swizzled A tile; the two groups take alternate
-//              K blocks. After the K loop warps 0-3 read the accumulator (TMEM lane r = weight
-//              row r) and store y
+//   warps 0-3, 8-11 decode: thread r of a group turns row r's 28-byte block into 128 FP16 values
+//              and stores them with tcgen05.st into lane r of tensor memory, where the MMA reads
+//              its A operand (the weights never pass through shared memory); the two groups take
+//              alternate K blocks. After the K loop warps 0-3 read the accumulator (TMEM lane r =
+//              weight row r) and store y
 //   warp 4     TMA: packed weight bytes (box 128 rows x 112 B = 4 groups) and activation tiles
 //   warp 5     allocates tensor memory and issues tcgen05.mma (one elected lane)
 //
@@ -38,13 +40,13 @@ namespace {
 constexpr int kTileW = 128;                 // weight rows per tile (UMMA M)
 constexpr int kPackGroups = 4;
 constexpr int kPackBytes = kTileW * kPackGroups * kBlockBytes;     // 14336
-constexpr int kATileBytes = kTileW * kGroup * 2;                   // 32768: two 64-wide swizzle atoms
 constexpr int kLutBytesG = 243 * 256;                              // 8-byte entries x 32 lanes
-constexpr int kGemmThreads = 320;            // 2 x 4 decode warps, one TMA warp, one MMA warp
-__host__ __device__ constexpr int gemm_stages(int nt) { return 2; }
+constexpr int kGemmThreads = 384;            // warps 0-3 and 8-11 decode, warp 4 TMA, warp 5 MMA (6, 7 idle)
+constexpr int kAStageCols = kGroup / 2;      // a 128-wide K block of FP16 weights = 64 tensor-memory columns
+__host__ __device__ constexpr int gemm_stages(int nt) { return nt > 128 ? 2 : 4; }
 // packed-byte buffers (4 K blocks each): small activation tiles leave room for a deep prefetch queue,
 // which is what hides HBM latency when the tensor work per K block is tiny
-__host__ __device__ constexpr int gemm_pack_bufs(int nt) { return nt <= 32 ? 6 : 2; }
+__host__ __device__ constexpr int gemm_pack_bufs(int nt) { return nt <= 64 ? 6 : 2; }
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 __host__ __device__ constexpr int perm_column(int p) {
@@ -128,13 +130,26 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
            (2ull << 61);
 }
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                         uint32_t accumulate) {
+// A operand in tensor memory (lane = weight row, 8 columns per K = 16 step), B in shared memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// 32 consecutive columns of this thread's tensor-memory lane <- 32 registers
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -169,12 +184,12 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     constexpr int kStagesG = gemm_stages(NT);
     constexpr int kPackBufs = gemm_pack_bufs(NT);
     constexpr int kBTileBytes = NT * kGroup * 2;
-    constexpr int kTmemCols = NT < 32 ? 32 : NT;
+    constexpr int kTmemCols = 512;                   // accumulator (NT columns) + A stages: one CTA per SM owns it all
+    constexpr int kAccCols = NT < 32 ? 32 : NT;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // swizzled operand tiles must start on a 1024-byte boundary of the shared window
     unsigned char *smem = smem_raw + ((1024u - ((uint32_t)__cvta_generic_to_shared(smem_raw) & 1023u)) & 1023u);
-    unsigned char *a_tiles = smem;                                       // kStagesG x 32 KiB, 1024-aligned
-    unsigned char *b_tiles = a_tiles + kStagesG * kATileBytes;           // kStagesG x NT*256
+    unsigned char *b_tiles = smem;                                       // kStagesG x NT*256, 1024-aligned
     unsigned char *packed = b_tiles + kStagesG * kBTileBytes;            // 2 x 14336
     unsigned char *lut = packed + kPackBufs * kPackBytes;                // 62208
     uint64_t *bars = reinterpret_cast<uint64_t *>(lut + kLutBytesG);
@@ -260,30 +275,26 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 ok = mbar_wait(bar(FULL_A + s), ph, prm.status) && mbar_wait(bar(FULL_B + s), ph, prm.status);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(a_tiles + s * kATileBytes);
+                const uint32_t a_tmem = tmem_base + (uint32_t)(kAccCols + s * kAStageCols);
                 const uint32_t b_addr = (uint32_t)__cvta_generic_to_shared(b_tiles + s * kBTileBytes);
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {       // four K = 16 steps per 64-wide swizzle atom
-                        const uint64_t da = umma_desc(a_addr + half * (kTileW * 128) + j * 32);
-                        const uint64_t db = umma_desc(b_addr + half * (NT * 128) + j * 32);
-                        umma_f16(tmem_base, da, db, idesc, (i > 0 || half > 0 || j > 0) ? 1u : 0u);
-                    }
+                for (int j = 0; j < 8; ++j) {           // eight K = 16 steps; B: two 64-wide swizzle atoms
+                    const uint64_t db = umma_desc(b_addr + (j >> 2) * (NT * 128) + (j & 3) * 32);
+                    umma_f16_ts(tmem_base, a_tmem + 8u * j, db, idesc, (i > 0 || j > 0) ? 1u : 0u);
                 }
                 umma_commit(bar(EMPTY + s));            // the stage is free once these MMAs have read it
             }
             if (ok) umma_commit(bar(ACCUM));
         }
+    } else if (warp == 6 || warp == 7) {
+        // idle: the decode groups must sit on warps whose index modulo 4 names their tensor-memory lanes
     } else {
         // ------------------------------------------------------------------ decode (thread = weight row)
         // two groups of four warps take alternate K blocks, so two stages are being filled at a time
         const int group = warp < 4 ? 0 : 1;
-        const int r = warp < 4 ? tid : tid - 192;        // 0..127
+        const int r = (warp & 3) * 32 + lane;            // 0..127 = tensor-memory lane (a warp reaches lanes 32*(warp%4)..)
         ok = mbar_wait(bar(LUT_BAR), 0, prm.status);
         const uint32_t lut_lane = (uint32_t)__cvta_generic_to_shared(lut) + (uint32_t)lane * 8u;
-        const uint32_t row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-        const uint32_t rx = (uint32_t)(r & 7);
         int pack_i = -1;
         for (int i = 0; i < n_kb && ok; ++i) {
             const int kb = kb_begin + i;
@@ -317,24 +328,41 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 const uint32_t addr = lut_lane + (byte << 8);
                 asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(e0[j]), "=r"(e1[j]) : "r"(addr));
             }
-            const uint32_t a_stage = (uint32_t)__cvta_generic_to_shared(a_tiles + s * kATileBytes) + row_off;
-            auto store_chunk = [&](int m, uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3) {
-                const uint32_t addr = a_stage + (uint32_t)((m >> 3) * (kTileW * 128)) + ((((uint32_t)m & 7u) ^ rx) << 4);
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v0), "r"(v1), "r"(v2), "r"(v3)
-                             : "memory");
-            };
+            // 64 registers = the row's 128 FP16 weights in decode order, written to this lane of tensor memory
+            const uint32_t a_taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) +
+                                     (uint32_t)(kAccCols + s * kAStageCols);
+            {
+                uint32_t v[32];
 #pragma unroll
-            for (int m = 0; m < 12; ++m)
-                store_chunk(m, prmt(pool, 0u, e0[2 * m]), prmt(pool, 0u, e1[2 * m]),
-                            prmt(pool, 0u, e0[2 * m + 1]), prmt(pool, 0u, e1[2 * m + 1]));
-            // trit-4 pairs: selector byte 0 from entry a (its byte 2), byte 1 from entry b (its byte 3)
-            auto c4pair = [&](int ja, int jb) { return prmt(pool, 0u, prmt(e0[ja], e0[jb], 0x4472)); };
-            store_chunk(12, prmt(pool, 0u, e0[24]), prmt(pool, 0u, e1[24]), prmt(pool, 0u, e0[25]),
-                        prmt(pool, 0u, prmt(e1[25], e0[0], 0x4470)));       // (tail trit 2, trit 4 of byte 0)
-            store_chunk(13, c4pair(1, 2), c4pair(3, 4), c4pair(5, 6), c4pair(7, 8));
-            store_chunk(14, c4pair(9, 10), c4pair(11, 12), c4pair(13, 14), c4pair(15, 16));
-            store_chunk(15, c4pair(17, 18), c4pair(19, 20), c4pair(21, 22), c4pair(23, 24));
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
+                for (int m = 0; m < 8; ++m) {
+                    v[4 * m] = prmt(pool, 0u, e0[2 * m]);
+                    v[4 * m + 1] = prmt(pool, 0u, e1[2 * m]);
+                    v[4 * m + 2] = prmt(pool, 0u, e0[2 * m + 1]);
+                    v[4 * m + 3] = prmt(pool, 0u, e1[2 * m + 1]);
+                }
+                tmem_store32(a_taddr, v);
+            }
+            {
+                // trit-4 pairs: selector byte 0 from entry a (its byte 2), byte 1 from entry b (its byte 3)
+                auto c4pair = [&](int ja, int jb) { return prmt(pool, 0u, prmt(e0[ja], e0[jb], 0x4472)); };
+                uint32_t v[32];
+#pragma unroll
+                for (int m = 8; m < 12; ++m) {
+                    v[4 * (m - 8)] = prmt(pool, 0u, e0[2 * m]);
+                    v[4 * (m - 8) + 1] = prmt(pool, 0u, e1[2 * m]);
+                    v[4 * (m - 8) + 2] = prmt(pool, 0u, e0[2 * m + 1]);
+                    v[4 * (m - 8) + 3] = prmt(pool, 0u, e1[2 * m + 1]);
+                }
+                v[16] = prmt(pool, 0u, e0[24]);
+                v[17] = prmt(pool, 0u, e1[24]);
+                v[18] = prmt(pool, 0u, e0[25]);
+                v[19] = prmt(pool, 0u, prmt(e1[25], e0[0], 0x4470));      // (tail trit 2, trit 4 of byte 0)
+#pragma unroll
+                for (int q = 0; q < 12; ++q) v[20 + q] = c4pair(2 * q + 1, 2 * q + 2);
+                tmem_store32(a_taddr + 32u, v);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(bar(FULL_A + s));
             if (last_of_chunk) mbar_arrive(bar(PACK_EMPTY + pack_i % kPackBufs));
         }
@@ -413,7 +441,7 @@ EncodeTiledFn gemm_encode_fn() {
     return fn;
 }
 
-int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
+int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M < 1024 ? 128 : 256; }
 
 int pick_splits(int M, int N, int K) {
     const int nt = token_tile(M);
@@ -433,7 +461,7 @@ size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 template <int NT>
 size_t gemm_smem_bytes() {
-    return (size_t)gemm_stages(NT) * kATileBytes + (size_t)gemm_stages(NT) * NT * kGroup * 2 +
+    return (size_t)gemm_stages(NT) * NT * kGroup * 2 +
            (size_t)gemm_pack_bufs(NT) * kPackBytes + kLutBytesG + 512 + 1024;
 }
 
@@ -524,7 +552,8 @@ int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, 
     int rc = nt == 16 ? launch_nt<16>(wmap, xmap, prm, grid, stream)
            : nt == 32 ? launch_nt<32>(wmap, xmap, prm, grid, stream)
            : nt == 64 ? launch_nt<64>(wmap, xmap, prm, grid, stream)
-                      : launch_nt<128>(wmap, xmap, prm, grid, stream);
+           : nt == 128 ? launch_nt<128>(wmap, xmap, prm, grid, stream)
+                       : launch_nt<256>(wmap, xmap, prm, grid, stream);
     if (rc != TQ1_OK) return rc;
     if (splits > 1) {
         const long long mn = (long long)M * N;

@@ -120,11 +120,12 @@ __device__ __forceinline__ uint32_t prmt_imm(uint32_t a, uint32_t b) {
     return d;
 }
 
-// Ring-buffer words: volatile so the loads stay behind the mbarrier wait.
+// Ring-buffer words. Not volatile: the address depends on the value returned by the barrier wait,
+// which keeps the loads behind it while leaving the compiler free to interleave the two sub-units.
 template <int OFF>
 __device__ __forceinline__ uint32_t lds_off(uint32_t addr) {
     uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF) : "memory");
+    asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
     return v;
 }
 
@@ -142,23 +143,23 @@ __device__ __forceinline__ void mma_bytes(int (&c)[4], uint32_t a0, uint32_t a1,
                                           uint32_t b0, uint32_t b1) {
     if (ZERO_C) {
         if (SIGNED_A)
-            asm volatile(
+            asm(
                 "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
         else
-            asm volatile(
+            asm(
                 "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
     } else {
         if (SIGNED_A)
-            asm volatile(
+            asm(
                 "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
         else
-            asm volatile(
+            asm(
                 "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -449,15 +450,16 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
         }
         const int s = i % kStages;
         const uint32_t parity = (uint32_t)(i / kStages) & 1u;
-        uint32_t spins = 0;
-        while (!mbar_try_wait(bar0 + 8u * s, parity)) {
+        uint32_t spins = 0, arrived;
+        while (!(arrived = mbar_try_wait(bar0 + 8u * s, parity))) {
             if (++spins > kMaxWaitSpins) {          // never hang: flag the failure and leave
                 if (lane == 0) atomicExch(status, 1u);
                 return;
             }
         }
         if (i == 0) PHASE(4);
-        const uint32_t tile_addr = ring_warp + (uint32_t)(s * kUnitBytes);
+        // (arrived >> 8) is zero, but only the hardware knows: the tile loads depend on the wait
+        const uint32_t tile_addr = ring_warp + (uint32_t)(s * kUnitBytes) + (arrived >> 8);
         float acc1 = 0.0f, acc2 = 0.0f;             // rows g and g+8, this lane's two groups
 #pragma unroll
         for (int sub = 0; sub < 2; ++sub) {
