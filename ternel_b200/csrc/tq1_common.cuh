@@ -16,13 +16,13 @@ constexpr int kFullBytes = 25;
 constexpr int kMaxFull = 242;
 constexpr int kMaxTail = 26;
 
-// Workspace layout shared by every linear kernel: [status word, 256 B][arrival counters, 64 KiB]
-// [kernel-specific scratch]. Only the counter region must be zero between calls, and no kernel
-// writes anything else there, so calls of any shape and kind can share one workspace.
+// Workspace layout shared by every linear kernel: [status words, 256 B][partial-sum slots of the
+// batch-1 kernel, 16 MiB][scratch of the batched kernel]. The slot region must be zero between
+// calls (its users leave it so) and no other kernel writes there, so calls of any shape and kind
+// can share one workspace. A batch-1 shape whose slots need more than the region takes the batched path.
 constexpr size_t kWsStatusBytes = 256;
-constexpr int kWsMaxCounters = 16384;
-constexpr size_t kWsCounterBytes = (size_t)kWsMaxCounters * sizeof(int);
-constexpr size_t kWsScratchOffset = kWsStatusBytes + kWsCounterBytes;
+constexpr size_t kWsSlotRegionBytes = (size_t)16 << 20;
+constexpr size_t kWsScratchOffset = kWsStatusBytes + kWsSlotRegionBytes;
 
 // Records a message for tq1_last_error() and returns `code`.
 int fail(int code, const char *fmt, ...);

@@ -9,13 +9,13 @@
 //
 // One CTA computes a tile of 128 weight rows x NT activation rows over a range of K:
 //   D[n][m] = sum_k W[n][k] * x[m][k]      (A = W tile, B = x tile, both K-major FP16)
-//   warps 0-3, 8-11 decode: thread r of a group turns row r's 28-byte block into 128 FP16 values
+//   warps 0-3, 4-7  decode: thread r of a group turns row r's 28-byte block into 128 FP16 values
 //              and stores them with tcgen05.st into lane r of tensor memory, where the MMA reads
 //              its A operand (the weights never pass through shared memory); the two groups take
 //              alternate K blocks. After the K loop warps 0-3 read the accumulator (TMEM lane r =
 //              weight row r) and store y
-//   warp 4     TMA: packed weight bytes (box 128 rows x 112 B = 4 groups) and activation tiles
-//   warp 5     allocates tensor memory and issues tcgen05.mma (one elected lane)
+//   warp 8     TMA: packed weight bytes (box 128 rows x 112 B = 4 groups) and activation tiles
+//   warp 9     allocates tensor memory and issues tcgen05.mma (one elected lane)
 //
 // K order. Five trits per byte do not pair up in natural order, so inside every 128-wide
 // group the K axis is permuted to a decode-friendly order (position p -> column pi(p) below)
@@ -41,12 +41,16 @@ constexpr int kTileW = 128;                 // weight rows per tile (UMMA M)
 constexpr int kPackGroups = 4;
 constexpr int kPackBytes = kTileW * kPackGroups * kBlockBytes;     // 14336
 constexpr int kLutBytesG = 243 * 256;                              // 8-byte entries x 32 lanes
-constexpr int kGemmThreads = 384;            // warps 0-3 and 8-11 decode, warp 4 TMA, warp 5 MMA (6, 7 idle)
+constexpr int kGemmThreads = 320;            // warps 0-3 and 4-7 decode, warp 8 TMA, warp 9 MMA
+constexpr int kTmaWarp = 8, kMmaWarp = 9;
 constexpr int kAStageCols = kGroup / 2;      // a 128-wide K block of FP16 weights = 64 tensor-memory columns
-__host__ __device__ constexpr int gemm_stages(int nt) { return nt > 128 ? 2 : 4; }
+// Small activation tiles: three stages and little shared memory, so that two CTAs share an SM and
+// hide each other's latencies. Large tiles: one CTA per SM with as many stages as fit.
+__host__ __device__ constexpr int gemm_stages(int nt) { return nt > 128 ? 2 : nt <= 16 ? 3 : 4; }
+__host__ __device__ constexpr int gemm_tmem_cols(int nt) { return nt <= 16 ? 256 : 512; }
 // packed-byte buffers (4 K blocks each): small activation tiles leave room for a deep prefetch queue,
 // which is what hides HBM latency when the tensor work per K block is tiny
-__host__ __device__ constexpr int gemm_pack_bufs(int nt) { return nt <= 64 ? 6 : 2; }
+__host__ __device__ constexpr int gemm_pack_bufs(int nt) { return (nt == 32 || nt == 64) ? 6 : 2; }
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 __host__ __device__ constexpr int perm_column(int p) {
@@ -178,13 +182,13 @@ struct GemmParams {
 };
 
 template <int NT>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads, NT <= 16 ? 2 : 1)
 tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                    const GemmParams prm) {
     constexpr int kStagesG = gemm_stages(NT);
     constexpr int kPackBufs = gemm_pack_bufs(NT);
     constexpr int kBTileBytes = NT * kGroup * 2;
-    constexpr int kTmemCols = 512;                   // accumulator (NT columns) + A stages: one CTA per SM owns it all
+    constexpr int kTmemCols = gemm_tmem_cols(NT);    // accumulator (NT columns) + A stages
     constexpr int kAccCols = NT < 32 ? 32 : NT;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // swizzled operand tiles must start on a 1024-byte boundary of the shared window
@@ -227,7 +231,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         mbar_expect_tx(bar(LUT_BAR), kLutBytesG);
         bulk_load((uint32_t)__cvta_generic_to_shared(lut), &g_gemm_lut, kLutBytesG, bar(LUT_BAR));
     }
-    if (warp == 5) {        // tensor-memory allocation is a warp-wide operation
+    if (warp == kMmaWarp) {        // tensor-memory allocation is a warp-wide operation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"((uint32_t)__cvta_generic_to_shared(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -238,7 +242,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
 
     bool ok = true;
-    if (warp == 4) {
+    if (warp == kTmaWarp) {
         // ------------------------------------------------------------------ TMA producers
         // lane 1 keeps the queue of packed-byte chunks full, lane 0 feeds the activation tiles;
         // the two run independently so that the weight prefetch can run several chunks ahead
@@ -264,7 +268,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 tma_load_2d(dst + NT * 128, &xmap, kb * kGroup + 64, m0, bar(FULL_B + s));
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             // instruction descriptor: FP32 accumulate, FP16 A and B, both K-major, M = 128, N = NT
@@ -286,8 +290,6 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             }
             if (ok) umma_commit(bar(ACCUM));
         }
-    } else if (warp == 6 || warp == 7) {
-        // idle: the decode groups must sit on warps whose index modulo 4 names their tensor-memory lanes
     } else {
         // ------------------------------------------------------------------ decode (thread = weight row)
         // two groups of four warps take alternate K blocks, so two stages are being filled at a time
@@ -397,7 +399,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
                      : "memory");
@@ -448,8 +450,10 @@ int pick_splits(int M, int N, int K) {
     const long long tiles = (long long)((N + kTileW - 1) / kTileW) * ((M + nt - 1) / nt);
     const int groups = K / kGroup;
     int splits = 1;
-    if (tiles < 148) {
-        splits = (int)((148 + tiles - 1) / tiles);
+    const long long slots = nt <= 16 ? 296 : 148;            // CTAs resident at once
+    if (tiles < slots) {
+        splits = (int)(slots / tiles);
+        if (splits < 1) splits = 1;
         const int max_splits = groups / 8 > 0 ? groups / 8 : 1;      // at least 8 groups per split
         if (splits > max_splits) splits = max_splits;
         if (splits > 32) splits = 32;

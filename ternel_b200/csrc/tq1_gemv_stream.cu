@@ -26,9 +26,10 @@
 // Units are numbered chunk-major and dealt out in contiguous ranges to the
 // warps of 148 persistent CTAs, so a warp keeps its B fragments (the
 // activation digits of one 512-wide K chunk) in registers while it streams row
-// tiles. Per-chunk partial sums go to a workspace; the warp that completes a
-// row tile (an arrival counter) adds the chunks in ascending order, so results
-// do not depend on timing.
+// tiles. Per-chunk partial sums go to workspace slots of eight bytes, the value
+// and a "present" flag written by one 64-bit store; a fixed owner per row tile
+// polls the slots, adds the chunks in ascending order (so results do not depend
+// on timing) and clears them for the next call.
 //
 // Lane roles inside mma.m16n8k32 (g = lane/4, q = lane%4): lane (g,q) decodes
 // half a block of row g and half a block of row g+8; q>>1 picks which of the
@@ -217,6 +218,22 @@ __device__ __forceinline__ void decode_stream(uint32_t wa, uint32_t wb, uint32_t
     r[17] = wd;
 }
 
+// Partial-sum slots: {FP32 value, flag} in one 64-bit word. A 64-bit store is a single access, so a
+// reader that finds the flag set also has the value; no fence and no second round trip is needed.
+constexpr unsigned long long kSlotPresent = 1ull << 32;
+__device__ __forceinline__ void slot_publish(unsigned long long *p, float v) {
+    const unsigned long long w = kSlotPresent | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long slot_read(const unsigned long long *p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+__device__ __forceinline__ void slot_clear(unsigned long long *p) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(0ull) : "memory");
+}
+
 // FP32 fallback for one block (row-major canonical bytes in shared memory) against
 // FP16 activations in global memory: multiplies every weight so that NaN and Inf
 // propagate exactly as in the reference.
@@ -238,8 +255,8 @@ template <bool OUT_F32>
 __global__ void __launch_bounds__(kThreads, 1)
 tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *__restrict__ x,
                        void *__restrict__ y, int N, int K, int tiles, int chunks,
-                       int *__restrict__ counters, float *__restrict__ partials,
-                       unsigned *__restrict__ status, const ShardDev shard) {
+                       unsigned long long *__restrict__ slots, unsigned *__restrict__ status,
+                       const ShardDev shard) {
     extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t window = (uint32_t)__cvta_generic_to_shared(smem);   // window address of smem[0]
     // carve-up: the ring below the table's fixed window address, everything else above the table
@@ -298,6 +315,10 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
             bulk_load(kLutWindowAddr, &g_lut_image, kLutBytes, lut_bar);
         }
     }
+#ifdef TQ1_WEIGHTS_BEFORE_WAIT
+    if (lane == 0)
+        while (issued < kStages - 1 && issued < n_units) issue_next();
+#endif
     // Let the next kernel in the stream start its own prologue as SMs free up, then wait until
     // everything before this kernel has finished before touching activations or the workspace.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -520,103 +541,65 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
         // quad: lanes q=0 (groups 0,1) and q=2 (groups 2,3) -> chunk partial in lane q=0
         acc1 += __shfl_down_sync(0xffffffffu, acc1, 2);
         acc2 += __shfl_down_sync(0xffffffffu, acc2, 2);
-        if (q == 0) {
-            float *mine = partials + ((size_t)c * tiles + t) * kTileRows;
-            __stcg(mine + g, acc1);
-            __stcg(mine + g + 8, acc2);
+        if (q == 0) {       // value and flag travel in one 64-bit store, so whoever sees the flag has the value
+            unsigned long long *mine = slots + ((size_t)c * tiles + t) * kTileRows;
+            slot_publish(mine + g, acc1);
+            slot_publish(mine + g + 8, acc2);
         }
         if (i == 0) PHASE(5);
         if (++t == tiles) { t = 0; ++c; }
     }
 
     PHASE(6);
-    // ---- publish: one release arrival per row tile --------------------------------------------------
-    // Row tile t is finished by a fixed owner, the warp that processed its chunk t % chunks: the
-    // owner waits (bounded) until all chunks have arrived. Leaving the reduction to whichever warp
-    // arrives last piles that work onto the slowest CTAs; with fixed owners every warp finishes
-    // about one tile per `chunks` units. All CTAs of the grid are resident (one per SM), so the
-    // owner's wait is for warps that are running.
-    __syncwarp();               // orders the partial-sum stores of all lanes before the releases below
+    // ---- finish row tiles ------------------------------------------------------------------------------
+    // Row tile t is finished by a fixed owner, the warp that processed its chunk t % chunks, so every
+    // warp finishes about one tile per `chunks` units. The owner polls the tile's slots (bounded) until
+    // every chunk's value is present. All CTAs of the grid are resident (one per SM), so the wait is
+    // for warps that are running. Lane (hf, r) adds chunks hf, hf+2, ... of row r in ascending order
+    // and one shuffle joins the two halves: the order of additions never depends on timing.
     PHASE(7);
     int tiles_finished = 0;
-    for (int i0 = 0; i0 < n_units; i0 += 32) {
-        int mine = 0;
-        if (i0 + lane < n_units) {
-            const int u = u_begin + i0 + lane;
-            const int cc = u / tiles, tt = u - cc * tiles;
-            // arrival: a release reduction (no return value, so nobody waits for the round trip)
-            asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(counters + tt) : "memory");
-            mine = (tt % chunks) == cc;
-        }
-        unsigned todo = __ballot_sync(0xffffffffu, mine);
-        tiles_finished += __popc(todo);
-        if (mine) {                 // wait for the other chunks of my tiles
-            const int tt = (u_begin + i0 + lane) % tiles;
-            uint32_t spins = 0;
-            for (;;) {
-                int v;
-                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counters + tt) : "memory");
-                if (v == chunks) break;
-                if (++spins > kMaxWaitSpins) { atomicExch(status, 5u); break; }
-            }
-        }
-        __syncwarp();               // the other lanes' loads below come after the acquiring lanes' loads
-        // Finish my tiles, two per pass. Lane (ts, cj, rq) adds chunks cj, cj+4, cj+8, ... of rows
-        // 4rq..4rq+3 of tile slot ts in ascending order (all loads of a batch issued before the first
-        // add), then a fixed shuffle tree combines the four chunk lanes: the order never depends on timing.
-        const int ts = lane >> 4, cj = (lane >> 2) & 3, rq = lane & 3;
+    {
+        const int r = lane & 15, hf = lane >> 4;
         const size_t stride = (size_t)tiles * kTileRows;
-        while (todo) {
-            const int b0 = __ffs(todo) - 1;
-            todo &= todo - 1;
-            int b1 = -1;
-            if (todo) { b1 = __ffs(todo) - 1; todo &= todo - 1; }
-            const int bit = ts ? b1 : b0;
-            const int tt = bit >= 0 ? (u_begin + i0 + bit) % tiles : 0;
-            float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (bit >= 0) {
-                const float *p = partials + (size_t)tt * kTileRows + 4 * rq;
-                for (int cc = cj; cc < chunks; cc += 48) {
-                    float4 v[12];
+        int cc = c_first, tt = t_first;
+        for (int i = 0; i < n_units; ++i) {
+            if (tt % chunks == cc) {                 // warp-uniform: this warp owns row tile tt
+                ++tiles_finished;
+                unsigned long long *p = slots + (size_t)tt * kTileRows + r;
+                float total = 0.0f;
+                for (int c0 = hf; c0 < chunks; c0 += 16) {
+                    unsigned long long v[8];
 #pragma unroll
-                    for (int k = 0; k < 12; ++k)
-                        v[k] = cc + 4 * k < chunks
-                                   ? __ldcg(reinterpret_cast<const float4 *>(p + (size_t)(cc + 4 * k) * stride))
-                                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    for (int k = 0; k < 8; ++k)
+                        v[k] = c0 + 2 * k < chunks ? slot_read(p + (size_t)(c0 + 2 * k) * stride) : kSlotPresent;
 #pragma unroll
-                    for (int k = 0; k < 12; ++k) {
-                        if (cc + 4 * k < chunks) {
-                            total.x += v[k].x; total.y += v[k].y; total.z += v[k].z; total.w += v[k].w;
+                    for (int k = 0; k < 8; ++k) {
+                        if (c0 + 2 * k < chunks) {
+                            uint32_t spins = 0;
+                            while ((v[k] >> 32) != 1ull) {
+                                if (++spins > kMaxWaitSpins) { atomicExch(status, 5u); break; }   // never hang
+                                v[k] = slot_read(p + (size_t)(c0 + 2 * k) * stride);
+                            }
+                            total += __uint_as_float((uint32_t)v[k]);
+                            slot_clear(p + (size_t)(c0 + 2 * k) * stride);        // ready for the next call
                         }
                     }
                 }
-            }
-#pragma unroll
-            for (int o = 4; o < 16; o <<= 1) {
-                total.x += __shfl_xor_sync(0xffffffffu, total.x, o);
-                total.y += __shfl_xor_sync(0xffffffffu, total.y, o);
-                total.z += __shfl_xor_sync(0xffffffffu, total.z, o);
-                total.w += __shfl_xor_sync(0xffffffffu, total.w, o);
-            }
-            if (bit >= 0 && cj == 0) {
-                const int row = tt * kTileRows + 4 * rq;
-                const float out[4] = {total.x, total.y, total.z, total.w};
-                if (shard.world > 1) {
-                    // fused all-gather: the finished rows go straight into every rank's gathered output
-                    for (int p2 = 0; p2 < shard.world; ++p2)
-                        for (int k = 0; k < 4; ++k)
-                            if (row + k < N) shard.peer_y[p2][row + k] = __float2half_rn(out[k]);
-                } else {
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        if (row + k < N) {
-                            if (OUT_F32) static_cast<float *>(y)[row + k] = out[k];
-                            else static_cast<__half *>(y)[row + k] = __float2half_rn(out[k]);
-                        }
+                total += __shfl_xor_sync(0xffffffffu, total, 16);
+                const int row = tt * kTileRows + r;
+                if (hf == 0 && row < N) {
+                    if (shard.world > 1) {
+                        // fused all-gather: the finished rows go straight into every rank's gathered output
+                        for (int p2 = 0; p2 < shard.world; ++p2) shard.peer_y[p2][row] = __float2half_rn(total);
+                    } else if (OUT_F32) {
+                        static_cast<float *>(y)[row] = total;
+                    } else {
+                        static_cast<__half *>(y)[row] = __float2half_rn(total);
                     }
                 }
-                if (rq == 0) counters[tt] = 0;     // ready for the next call
             }
+            if (++tt == tiles) { tt = 0; ++cc; }
         }
     }
     if (shard.world > 1 && tiles_finished > 0) {
@@ -656,15 +639,13 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-constexpr size_t kHeaderBytes = kWsStatusBytes;
-constexpr int kMaxTiles = kWsMaxCounters;
-constexpr size_t kCounterBytes = kWsCounterBytes;
+constexpr int kMaxTiles = 16384;
 
 }  // namespace
 
 bool gemv_stream_shape_ok(int N, int K) {
     return N >= 1 && (N + kTileRows - 1) / kTileRows <= kMaxTiles && K % (kChunkGroups * kGroup) == 0 &&
-           K / (kChunkGroups * kGroup) <= 256;
+           K / (kChunkGroups * kGroup) <= 256 && gemv_stream_workspace_bytes(N, K) <= kWsScratchOffset;
 }
 
 bool gemv_stream_supported(const uint8_t *blocks, int N, int K) {
@@ -674,7 +655,7 @@ bool gemv_stream_supported(const uint8_t *blocks, int N, int K) {
 size_t gemv_stream_workspace_bytes(int N, int K) {
     const size_t tiles = (N + kTileRows - 1) / kTileRows;
     const size_t chunks = K / (kChunkGroups * kGroup);
-    return kHeaderBytes + kCounterBytes + chunks * tiles * kTileRows * sizeof(float);
+    return kWsStatusBytes + chunks * tiles * kTileRows * sizeof(unsigned long long);
 }
 
 int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K,
@@ -696,8 +677,7 @@ int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f
 
     unsigned char *ws = static_cast<unsigned char *>(workspace);
     unsigned *status = reinterpret_cast<unsigned *>(ws);
-    int *counters = reinterpret_cast<int *>(ws + kHeaderBytes);
-    float *partials = reinterpret_cast<float *>(ws + kHeaderBytes + kCounterBytes);
+    unsigned long long *slots = reinterpret_cast<unsigned long long *>(ws + kWsStatusBytes);
 
     static int sm_count = 0;
     static size_t smem_bytes = 0;
@@ -743,8 +723,8 @@ int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f
         sd.done_counter = status + 1;       // second word of the workspace header, zero between calls
     }
     cudaError_t err =
-        y_f32 ? cudaLaunchKernelEx(&cfg, kf, map, xc, y, N, K, tiles, chunks, counters, partials, status, sd)
-              : cudaLaunchKernelEx(&cfg, kh, map, xc, y, N, K, tiles, chunks, counters, partials, status, sd);
+        y_f32 ? cudaLaunchKernelEx(&cfg, kf, map, xc, y, N, K, tiles, chunks, slots, status, sd)
+              : cudaLaunchKernelEx(&cfg, kh, map, xc, y, N, K, tiles, chunks, slots, status, sd);
     if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: launch");
     err = cudaGetLastError();
     if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: launch");
@@ -757,10 +737,10 @@ int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f
 // Some hosts cannot give this library scratch memory at call time: code that runs inside a
 // stream-capture region (where cudaMalloc is illegal), plugin hosts whose whole device budget
 // was handed out when the model was loaded, and real-time loops that must not touch the
-// allocator. For them the scratch of the streaming GEMV (status word, arrival counters,
-// per-chunk partial sums) lives in this fixed array, which every GPU that loads the library
+// allocator. For them the scratch of the streaming GEMV (status word and per-chunk
+// partial-sum slots) lives in this fixed array, which every GPU that loads the library
 // holds until the process exits.
-constexpr size_t kNoAllocScratchBytes = 2u << 20;       // 2 MiB: N*K up to about 2.6e8 weights
+constexpr size_t kNoAllocScratchBytes = 2u << 20;       // 2 MiB: N*K up to about 1.3e8 weights
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 namespace {
@@ -790,9 +770,9 @@ int gemv_noalloc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, in
         g_noalloc_ptr[dev] = ptr;
     }
     unsigned char *scratch = static_cast<unsigned char *>(g_noalloc_ptr[dev]);
-    // The array keeps whatever the last call left: the counters (and the status word) must start at zero.
-    err = cudaMemsetAsync(scratch, 0, kWsScratchOffset, stream);
-    if (err != cudaSuccess) return cuda_fail(err, "tq1_gemv_f16_noalloc: clearing the counters");
+    // The array keeps whatever the last call left: the status word and the slots this shape uses start at zero.
+    err = cudaMemsetAsync(scratch, 0, need, stream);
+    if (err != cudaSuccess) return cuda_fail(err, "tq1_gemv_f16_noalloc: clearing the scratch");
     return launch_gemv_stream(blocks, x, y, y_f32, N, K, scratch, stream);
 }
 

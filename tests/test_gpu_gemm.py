@@ -9,7 +9,9 @@ from tests.gpu_util import POWERS, random_blocks, run_linear
 
 pytestmark = pytest.mark.gpu
 
-F32_TOL = 1e-5
+# The required bound is 1e-3 (max |got - want| / max |want|). The tensor cores add the FP16 products of a
+# 5120- to 17408-long row in FP32 within one accumulator, which lands between 3e-6 and 1.1e-5 on these cases.
+F32_TOL = 5e-5
 F16_TOL = 2e-3
 
 
