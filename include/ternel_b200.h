@@ -100,7 +100,13 @@ size_t tq1_linear_workspace_bytes(int M, int N, int K);
  *             aligned (may be NULL when that is 0). It must be zero-filled
  *             once before its first use; every call leaves it ready for the
  *             next one, of any shape. Calls that may overlap on the GPU
- *             (different streams) need separate workspaces.
+ *             (different streams) need separate workspaces. Layout: status
+ *             words (256 B; word 0 becomes non-zero if a bounded wait inside
+ *             a kernel ran out), then 16 MiB of partial-sum slots for M == 1
+ *             (eight bytes per row and 512-wide K chunk: the value and a
+ *             "present" flag in one 64-bit word, cleared again by the call
+ *             that used them), then the scratch of the M >= 2 kernels. After
+ *             a non-zero status, zero-fill the workspace again.
  * The kernel is chosen from M: 1 => streaming GEMV, 2..16 => small-batch
  * split-K GEMV, larger => tiled GEMM. Illegal code bytes must have been
  * rejected at load (tq1_validate_blocks*): the kernels carry no clamp. */
@@ -142,16 +148,16 @@ int tq1_linear_f16_sharded(const uint8_t *blocks, const void *x, const tq1_shard
  * reference: it exists for hosts that must not allocate at call time -- code running inside a
  * stream-capture region (cudaMalloc is illegal there), plugin hosts whose device budget was
  * fixed when the model was loaded, real-time loops that stay away from the allocator.
- * Same arithmetic and result as tq1_linear_f16 with M == 1, but the scratch (status word,
- * arrival counters, per-chunk partial sums) lives in a 2 MiB array built into the library,
+ * Same arithmetic and result as tq1_linear_f16 with M == 1, but the scratch (status words
+ * and per-chunk partial-sum slots) lives in a 2 MiB array built into the library,
  * which every GPU that loads the library holds until the process exits.
- *   - Limits: K % 512 == 0, blocks 16-byte aligned, and N*K/128 + 65,792 bytes of scratch must
- *     fit in 2 MiB (N*K up to about 2.6e8 weights, e.g. 34816 x 5120); larger shapes are
+ *   - Limits: K % 512 == 0, blocks 16-byte aligned, and N*K/64 + 256 bytes of scratch must
+ *     fit in 2 MiB (N*K up to about 1.3e8 weights, e.g. 5120 x 17408); larger shapes are
  *     rejected with TQ1_ERR_WORKSPACE and a message, nothing is launched.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress) with that device current; make that first call outside any
  *     stream capture.
- *   - Every call on a device shares the one array and clears its counters on `stream` first,
+ *   - Every call on a device shares the one array and clears the part it uses on `stream` first,
  *     so calls that may overlap on the GPU (different streams) race with each other; keep
  *     them on one stream or order them with events.
  *   - Calls no cudaMalloc, cudaFree or allocating library routine. */

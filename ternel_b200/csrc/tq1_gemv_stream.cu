@@ -315,10 +315,6 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
             bulk_load(kLutWindowAddr, &g_lut_image, kLutBytes, lut_bar);
         }
     }
-#ifdef TQ1_WEIGHTS_BEFORE_WAIT
-    if (lane == 0)
-        while (issued < kStages - 1 && issued < n_units) issue_next();
-#endif
     // Let the next kernel in the stream start its own prologue as SMs free up, then wait until
     // everything before this kernel has finished before touching activations or the workspace.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -356,9 +352,10 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
         x4v[cl] = live ? __half2float(__ldg(xc + fifth)) : 0.0f;
     }
     // The activation loads are in flight: now start this warp's weight tiles. (Issued the other way
-    // round, the few activation bytes queue behind megabytes of weight traffic and arrive 1-2 us late.)
-    if (lane == 0)
-        while (issued < kStages - 1 && issued < n_units) issue_next();
+    // round, or before the wait above, the few activation bytes queue behind megabytes of weight
+    // traffic and arrive 1-2 us late.)
+    // One tile per warp for now, so that every warp's first tile is near the head of the queue.
+    if (lane == 0 && issued < n_units) issue_next();
     for (int i = tid; i < (int)(kBtabBytes / 16); i += kThreads)
         reinterpret_cast<uint4 *>(btab)[i] = make_uint4(0u, 0u, 0u, 0u);
 
@@ -381,6 +378,9 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     }
     __syncthreads();
     PHASE(2);
+    // every warp's first tile is on its way: now queue the rest of the ring behind them
+    if (lane == 0)
+        while (issued < kStages - 1 && issued < n_units) issue_next();
     {
         const int hh = bj < 14 ? 0 : 1;                    // which half-block lane decodes it
         const int slot = hh ? bj - 12 : bj;
@@ -639,27 +639,58 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-constexpr int kMaxTiles = 16384;
 
 }  // namespace
 
 bool gemv_stream_shape_ok(int N, int K) {
-    return N >= 1 && (N + kTileRows - 1) / kTileRows <= kMaxTiles && K % (kChunkGroups * kGroup) == 0 &&
-           K / (kChunkGroups * kGroup) <= 256 && gemv_stream_workspace_bytes(N, K) <= kWsScratchOffset;
+    return N >= 1 && K % (kChunkGroups * kGroup) == 0 && K / (kChunkGroups * kGroup) <= 256;
 }
 
 bool gemv_stream_supported(const uint8_t *blocks, int N, int K) {
     return gemv_stream_shape_ok(N, K) && (reinterpret_cast<uintptr_t>(blocks) & 15) == 0;
 }
 
+namespace {
+// Rows one launch may cover: its partial-sum slots (8 bytes per row and K chunk) must fit the slot region.
+int rows_per_launch(int N, int K) {
+    const size_t chunks = K / (kChunkGroups * kGroup);
+    const size_t cap = kWsSlotRegionBytes / (chunks * sizeof(unsigned long long)) / kTileRows * kTileRows;
+    if ((size_t)N <= cap) return N;
+    const size_t launches = ((size_t)N + cap - 1) / cap;
+    return (int)((((size_t)N + launches - 1) / launches + kTileRows - 1) / kTileRows * kTileRows);
+}
+}  // namespace
+
 size_t gemv_stream_workspace_bytes(int N, int K) {
-    const size_t tiles = (N + kTileRows - 1) / kTileRows;
+    const size_t tiles = (rows_per_launch(N, K) + kTileRows - 1) / kTileRows;
     const size_t chunks = K / (kChunkGroups * kGroup);
     return kWsStatusBytes + chunks * tiles * kTileRows * sizeof(unsigned long long);
 }
 
+static int launch_gemv_rows_block(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K,
+                                  void *workspace, cudaStream_t stream, const ShardDev *shard);
+
+// Very tall matrices (an output head of a few hundred thousand rows) run as consecutive launches over
+// row ranges, which reuse the same slots: each launch leaves them cleared.
 int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K,
                        void *workspace, cudaStream_t stream, const ShardDev *shard) {
+    const int step = rows_per_launch(N, K);
+    if (step < N && shard)
+        return fail(TQ1_ERR_INVALID, "tq1_linear_f16_sharded: a shard of %d rows is too tall for one launch", N);
+    const size_t row_bytes = (size_t)(K / kGroup) * kBlockBytes;
+    for (int n0 = 0; n0 < N; n0 += step) {
+        const int rows = N - n0 < step ? N - n0 : step;
+        void *yb = y_f32 ? static_cast<void *>(static_cast<float *>(y) + n0)
+                         : static_cast<void *>(static_cast<__half *>(y) + n0);
+        const int rc = launch_gemv_rows_block(blocks + (size_t)n0 * row_bytes, x, y ? yb : nullptr, y_f32, rows, K,
+                                              workspace, stream, shard);
+        if (rc != TQ1_OK) return rc;
+    }
+    return TQ1_OK;
+}
+
+static int launch_gemv_rows_block(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K,
+                                  void *workspace, cudaStream_t stream, const ShardDev *shard) {
     EncodeTiledFn encode = encode_fn();
     if (!encode) return fail(TQ1_ERR_CUDA, "tq1_linear_f16: cuTensorMapEncodeTiled is unavailable");
     const int tiles = (N + kTileRows - 1) / kTileRows;
@@ -751,8 +782,8 @@ void *g_noalloc_ptr[kMaxDevices] = {};     // device address of g_noalloc_scratc
 int gemv_noalloc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K, cudaStream_t stream) {
     if (!gemv_stream_supported(blocks, N, K))
         return fail(TQ1_ERR_INVALID,
-                    "tq1_gemv_f16_noalloc: needs K %% 512 == 0, 16-byte aligned blocks and at most %d rows "
-                    "(got N=%d K=%d)", kMaxTiles * kTileRows, N, K);
+                    "tq1_gemv_f16_noalloc: needs K %% 512 == 0, at most 256 K chunks and 16-byte aligned blocks "
+                    "(got N=%d K=%d)", N, K);
     const size_t need = gemv_stream_workspace_bytes(N, K);
     if (need > kNoAllocScratchBytes)
         return fail(TQ1_ERR_WORKSPACE,

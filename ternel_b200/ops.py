@@ -43,7 +43,7 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
     index = device.index if device.index is not None else torch.cuda.current_device()
     buf = _workspaces.get(index)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)   # counters start at zero
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)   # slots start at zero
         _workspaces[index] = buf
     return buf
 

@@ -3,6 +3,7 @@
 import numpy as np
 import pytest
 
+from oracle import c_oracle
 from oracle import tq1_oracle as o
 from tests.gpu_util import POWERS, random_blocks, run_linear
 
@@ -121,7 +122,7 @@ def test_ragged_row_counts(rows, columns):
 
 
 def test_workspace_is_reusable_across_shapes():
-    """Alternating shapes on one workspace: the arrival counters must return to zero after each call."""
+    """Alternating shapes on one workspace: the partial-sum slots must be clear again after each call."""
     shapes = ((5120, 5120), (64, 512), (1024, 5120), (5120, 17408), (48, 5120))
     cases = []
     for rows, columns in shapes:
@@ -144,3 +145,20 @@ def test_workspace_is_shared_with_the_batched_kernels():
         run_linear(blocks, x300)
         assert np.array_equal(run_linear(blocks, x1), first1)
         assert np.array_equal(run_linear(blocks, x8), first8)
+
+
+def test_very_tall_matrix_runs_as_row_ranges():
+    """An output head taller than one launch's slot region (16 MiB / (8 B x K chunks) rows) is split
+    into row ranges; a tall, narrow stand-in keeps the oracle fast."""
+    rows, columns = 300_000, 512 * 8          # 8 chunks: 262,144 rows per launch
+    rng = np.random.default_rng(11)
+    blocks = np.empty((rows, columns // 128, 28), dtype=np.uint8)
+    blocks[:, :, 0:2] = rng.standard_normal((rows, columns // 128)).astype(np.float16).view(np.uint8).reshape(
+        rows, columns // 128, 2)
+    blocks[:, :, 2:27] = rng.integers(0, 243, (rows, columns // 128, 25), dtype=np.uint8)
+    blocks[:, :, 27] = rng.integers(0, 27, (rows, columns // 128), dtype=np.uint8)
+    x = rng.standard_normal((1, columns)).astype(np.float16)
+    want = c_oracle.matmul_f32(blocks, x.astype(np.float32), rows=rows, columns=columns)
+    got = run_linear(blocks, x)
+    assert got.shape == (1, rows)
+    assert o.normalised_error(got, want) < 1e-5
