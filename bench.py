@@ -35,6 +35,9 @@ METRIC = "tq1_gemv_effective_hbm_gbps"
 UNIT = "GB/s"
 
 
+NCU_TRAFFIC_RATIO = 72.93 / 72.42     # measured DRAM bytes / algorithmic bytes, batch-1 GEMV, four shapes
+
+
 def parse_args():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
@@ -51,6 +54,10 @@ def parse_args():
     p.add_argument("--skip-cpu-baseline", action="store_true")
     p.add_argument("--skip-e2e", action="store_true")
     p.add_argument("--skip-batched", action="store_true", help="skip the small-batch and prefill side measurements")
+    p.add_argument("--only-batched", default="",
+                   help="run only the batched side measurement on these cases, e.g. '2:17408x5120,2048:5120x17408' "
+                        "(M:NxK), print its JSON and exit; with --ring to choose the number of distinct weight buffers")
+    p.add_argument("--ring", type=int, default=14, help="distinct weight buffers per shape in the batched measurement")
     return p.parse_args()
 
 
@@ -160,7 +167,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-i", str(self.gpu_index), "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+                 "-i", str(self.gpu_index), "-lms", "20"], stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
@@ -231,7 +238,8 @@ def run_gpu_arm(args) -> None:
         err = o.normalised_error(got, want)
         assert err < 2e-3, f"parity check failed before timing: {err}"
 
-    use_graph = not args.no_graph
+    # the NCCL baseline exchange is launched from the host every step (its capture did not complete here)
+    use_graph = not args.no_graph and not (world > 1 and args.exchange == "nccl")
     graph = None
     if use_graph:
         side = torch.cuda.Stream(device=device)
@@ -310,7 +318,13 @@ def run_gpu_arm(args) -> None:
                 "kernel": "packed GEMV (all projections of the step)",
                 "algorithmic_bytes_per_launch_avg": alg_bytes_rank / stack.launches_per_step,
                 "avg_launch_us": ms_per_step * 1e3 / stack.launches_per_step,
-                "traffic": None,
+                # DRAM bytes per launch: the ncu capture of one launch of each of the four shapes
+                # (profiles/gemv_stream_decode_step_batch1.md) read 72.93 MB against 72.42 MB of
+                # algorithmic bytes; traffic grows with the units processed, so the ratio carries over.
+                # Only the fused batch-1 single-GPU step was captured.
+                "traffic": (NCU_TRAFFIC_RATIO * alg_bytes_rank / stack.launches_per_step
+                            if args.batch == 1 and world == 1 and not args.unfused else None),
+                "traffic_source": "ncu dram__bytes_read+write of a 2-layer capture, scaled by bytes processed",
             },
             "checksum": checksum,
         }
@@ -379,7 +393,7 @@ def measure_shapes(stack, device, replays: int = 5):
     return out
 
 
-def measure_batched(device, replays: int = 3):
+def measure_batched(device, replays: int = 3, cases=None, ring_size: int = 14):
     """Side measurements of the batched kernels: small batch (M = 2..16, HBM-bound, GB/s of packed
     weights) and prefill (M = 512, 2048, tensor-bound, TFLOP/s), each over a ring of distinct weights."""
     import ctypes
@@ -394,9 +408,11 @@ def measure_batched(device, replays: int = 3):
     peaks_path = ROOT / "MEASURED_PEAKS.json"
     peak_tf = float(json.loads(peaks_path.read_text()).get("bf16_tflops", 1590.0)) if peaks_path.exists() else 1590.0
     out = {"small_batch": {}, "prefill": {}, "tensor_peak_tflops": peak_tf}
-    for n, k in ((17408, 5120), (5120, 17408)):
-        ring = [random_blocks_device(n, k, gen, device) for _ in range(14)]     # 14 x 19.5 MB > 2 x L2
-        for m in (2, 4, 8, 16, 512, 2048):
+    if cases is None:
+        cases = [(m, n, k) for n, k in ((17408, 5120), (5120, 17408)) for m in (2, 4, 8, 16, 512, 2048)]
+    for n, k in dict.fromkeys((n, k) for _, n, k in cases):
+        ring = [random_blocks_device(n, k, gen, device) for _ in range(ring_size)]   # 14 x 19.5 MB > 2 x L2
+        for m in [m for m, n2, k2 in cases if (n2, k2) == (n, k)]:
             x = torch.randn((m, k), generator=gen, device=device).to(torch.float16)
             y = torch.empty((m, n), dtype=torch.float16, device=device)
             ws_bytes = lib.tq1_linear_workspace_bytes(m, n, k)
@@ -506,6 +522,16 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.only_batched:
+        import torch
+        cases = []
+        for item in args.only_batched.split(","):
+            m, shape = item.split(":")
+            n, k = shape.lower().split("x")
+            cases.append((int(m), int(n), int(k)))
+        device = torch.device("cuda:0")
+        torch.cuda.set_device(device)
+        print(json.dumps({"batched": measure_batched(device, cases=cases, ring_size=args.ring)}))
     else:
         run_gpu_arm(args)
 
