@@ -284,6 +284,8 @@ def run_gpu_arm(args) -> None:
 
     per_shape = measure_shapes(stack, device) if world == 1 else None
     batched = measure_batched(device) if world == 1 and not args.skip_batched else None
+    if batched is not None and args.batch == 1:
+        batched["decode_step_batch8"] = measure_step_batch8(args, stack, device)
 
     # end-to-end through the public operator API with host buffers
     e2e = None
@@ -451,6 +453,40 @@ def measure_batched(device, replays: int = 3, cases=None, ring_size: int = 14):
             del graph, x, y, ws
         del ring
     return out
+
+
+def measure_step_batch8(args, stack, device, replays: int = 10):
+    """The same 64-layer step with eight sequences per step (the small-batch kernel), over the same
+    resident weights; graph-timed like the headline step."""
+    import torch
+    from ternel_b200.stack import LayerStack
+
+    stack8 = LayerStack(layers=args.layers, batch=8, vocab=stack.vocab, device=device, seed=0,
+                        fused=stack.fused, weights_from=stack)
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        stack8.step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        stack8.step()
+    for _ in range(3):
+        graph.replay()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(replays):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / replays
+    status = int(stack8.workspace[:4].view(torch.int32)[0].item())
+    if status != 0:
+        raise SystemExit(f"batch-8 step: a bounded device wait ran out (status word {status})")
+    return {"ms_per_step": ms, "tokens_per_s": 8 / (ms / 1e3),
+            "gbps": stack8.algorithmic_bytes_per_step / (ms / 1e3) / 1e9, "checksum": stack8.checksum()}
 
 
 def measure_e2e(args, stack, device, world, barrier):

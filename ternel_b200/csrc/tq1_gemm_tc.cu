@@ -7,13 +7,19 @@
 // the reference's GEMM, the group scale is folded into the FP16 weight, which is exact:
 // (c-1)*s is -s, 0 or +s (src/ternel_mlx/kernels.py:435-440).
 //
-// One CTA computes a tile of 128 weight rows x NT activation rows over a range of K:
+// An output tile is 128 weight rows x NT activation rows:
 //   D[n][m] = sum_k W[n][k] * x[m][k]      (A = W tile, B = x tile, both K-major FP16)
+// Persistent CTAs (one per SM, two for the 16-token tiles) share the work stream-K fashion: the
+// (tile, K block) iterations, numbered tile-major, are cut into equal contiguous ranges, so every CTA
+// does the same number of K blocks whatever the tile count. A range is a sequence of segments; a
+// segment that covers a tile's whole K range is stored as the result, a partial one (only a CTA's
+// first or last) goes to the workspace as FP32 and a fix-up kernel adds the pieces of such a tile
+// in ascending K order (deterministic).
 //   warps 0-3, 4-7  decode: thread r of a group turns row r's 28-byte block into 128 FP16 values
 //              and stores them with tcgen05.st into lane r of tensor memory, where the MMA reads
 //              its A operand (the weights never pass through shared memory); the two groups take
-//              alternate K blocks. After the K loop warps 0-3 read the accumulator (TMEM lane r =
-//              weight row r) and store y
+//              alternate K blocks. After a segment's K loop warps 0-3 read the accumulator (TMEM
+//              lane r = weight row r) and store it, then release it to the MMA warp
 //   warp 8     TMA: packed weight bytes (box 128 rows x 112 B = 4 groups) and activation tiles
 //   warp 9     allocates tensor memory and issues tcgen05.mma (one elected lane)
 //
@@ -25,9 +31,6 @@
 //   p = 100,101,102        : the three tail trits           (columns 125,126,127)
 //   p = 103                : trit 4 of code byte 0          (column 4)
 //   p = 104+q  (q<24)      : trit 4 of code byte q+1        (column 5(q+1)+4)
-//
-// Small grids are filled by splitting K over gridDim.z; the FP32 partial tiles go to the
-// workspace and a second kernel adds them in ascending split order (deterministic).
 #include <cuda.h>
 #include <stdlib.h>
 
@@ -171,17 +174,40 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr) : "memory");
 }
 
+// Stream-K work split: the (output tile, K block) iterations, numbered tile-major, are dealt out in equal
+// contiguous ranges to the CTAs. A range is a sequence of segments (tile, first K block, K blocks); only a
+// CTA's first and last segment can cover part of a tile's K range.
+//
+// With fewer tiles than CTA slots the ranges are instead `splits` equal parts of every tile, cut at
+// multiples of four K blocks (the packed-byte chunk), so that no CTA straddles two tiles or loads a
+// chunk it uses only in part.
+struct WorkSplit {
+    int total_iters, ctas, groups, splits;      // splits == 0: equal contiguous ranges
+    int quot, rem;                              // total_iters = ctas * quot + rem: the first `rem` ranges get one more
+    __host__ __device__ int first_iter(int cta) const {
+        if (cta >= ctas) return total_iters;
+        if (splits == 0) return cta * quot + (cta < rem ? cta : rem);
+        const int tile = cta / splits, part = cta - tile * splits;
+        int kb = groups * part / splits;
+        if (groups >= 4 * splits) kb &= ~3;
+        return tile * groups + kb;
+    }
+};
+
 struct GemmParams {
     const __half *xperm;      // permuted activations [M][K]
-    void *y;                  // final output [M][N] (FP16/FP32) when splits == 1
-    float *partials;          // [splits][M][N] when splits > 1
+    void *y;                  // final output [M][N] (FP16/FP32)
+    float *partials;          // [2 * CTAs][NT][128] FP32: K-partial tiles of the CTAs' first and last segments
     unsigned *status;
     int M, N, K;
-    int splits;
+    int tiles_m;              // activation tiles; output tile t covers weight tile t / tiles_m, token tile t % tiles_m
+    WorkSplit work;           // which (tile, K block) iterations each CTA takes
     int y_f32;
 };
 
-template <int NT>
+// PERSIST = false: the CTA's range is known to be one segment (the equal-parts split), and the
+// segment loops below compile to straight-line code.
+template <int NT, bool PERSIST>
 __global__ void __launch_bounds__(kGemmThreads, NT <= 16 ? 2 : 1)
 tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                    const GemmParams prm) {
@@ -199,20 +225,17 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     uint64_t *bars = reinterpret_cast<uint64_t *>(lut + kLutBytesG);
     // barrier indices
     constexpr int FULL_A = 0, FULL_B = FULL_A + kStagesG, EMPTY = FULL_B + kStagesG, PACK_FULL = EMPTY + kStagesG,
-                  PACK_EMPTY = PACK_FULL + kPackBufs, ACCUM = PACK_EMPTY + kPackBufs, LUT_BAR = ACCUM + 1,
-                  NUM_BARS = LUT_BAR + 1;
+                  PACK_EMPTY = PACK_FULL + kPackBufs, ACCUM = PACK_EMPTY + kPackBufs, ACC_FREE = ACCUM + 1,
+                  LUT_BAR = ACC_FREE + 1, NUM_BARS = LUT_BAR + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NUM_BARS);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
-    const int n0 = blockIdx.x * kTileW;                 // first weight row of the tile
-    const int m0 = blockIdx.y * NT;                     // first activation row
     const int groups = prm.K / kGroup;
-    const int kb_begin = (int)((long long)groups * blockIdx.z / prm.splits);
-    const int kb_end = (int)((long long)groups * (blockIdx.z + 1) / prm.splits);
-    const int n_kb = kb_end - kb_begin;
+    const int it_begin = prm.work.first_iter(blockIdx.x);
+    const int it_end = prm.work.first_iter(blockIdx.x + 1);
 
     if (tid == 0) {
         for (int s = 0; s < kStagesG; ++s) {
@@ -225,6 +248,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             mbar_init(bar(PACK_EMPTY + p), 256);
         }
         mbar_init(bar(ACCUM), 1);
+        mbar_init(bar(ACC_FREE), 128);
         mbar_init(bar(LUT_BAR), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -247,48 +271,70 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         // lane 1 keeps the queue of packed-byte chunks full, lane 0 feeds the activation tiles;
         // the two run independently so that the weight prefetch can run several chunks ahead
         if (lane == 1) {
-            const int first_chunk = kb_begin / kPackGroups, last_chunk = (kb_end - 1) / kPackGroups;
-            for (int c = first_chunk, pack_i = 0; c <= last_chunk && ok; ++c, ++pack_i) {
-                const int p = pack_i % kPackBufs;
-                ok = mbar_wait(bar(PACK_EMPTY + p), ((uint32_t)(pack_i / kPackBufs) & 1u) ^ 1u, prm.status);
-                if (!ok) break;
-                mbar_expect_tx(bar(PACK_FULL + p), kPackBytes);
-                tma_load_2d((uint32_t)__cvta_generic_to_shared(packed + p * kPackBytes), &wmap,
-                            c * (kPackGroups * kBlockBytes), n0, bar(PACK_FULL + p));
-            }
+            int pack_i = 0, it = it_begin;
+            do {
+                const int tile = it / groups, kb0 = it - tile * groups;
+                const int len = min(groups - kb0, it_end - it);
+                const int n0 = (tile / prm.tiles_m) * kTileW;
+                const int first_chunk = kb0 / kPackGroups, last_chunk = (kb0 + len - 1) / kPackGroups;
+                for (int c = first_chunk; c <= last_chunk && ok; ++c, ++pack_i) {
+                    const int p = pack_i % kPackBufs;
+                    ok = mbar_wait(bar(PACK_EMPTY + p), ((uint32_t)(pack_i / kPackBufs) & 1u) ^ 1u, prm.status);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(PACK_FULL + p), kPackBytes);
+                    tma_load_2d((uint32_t)__cvta_generic_to_shared(packed + p * kPackBytes), &wmap,
+                                c * (kPackGroups * kBlockBytes), n0, bar(PACK_FULL + p));
+                }
+                it += len;
+            } while (PERSIST && it < it_end && ok);
         } else if (lane == 0) {
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int kb = kb_begin + i;
-                const int s = i % kStagesG;
-                ok = mbar_wait(bar(EMPTY + s), ((uint32_t)(i / kStagesG) & 1u) ^ 1u, prm.status);
-                if (!ok) break;
-                mbar_expect_tx(bar(FULL_B + s), kBTileBytes);
-                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(b_tiles + s * kBTileBytes);
-                tma_load_2d(dst, &xmap, kb * kGroup, m0, bar(FULL_B + s));
-                tma_load_2d(dst + NT * 128, &xmap, kb * kGroup + 64, m0, bar(FULL_B + s));
-            }
+            int i = 0, it = it_begin;
+            do {
+                const int tile = it / groups, kb0 = it - tile * groups;
+                const int len = min(groups - kb0, it_end - it);
+                const int m0 = (tile % prm.tiles_m) * NT;
+                for (int kb = kb0; kb < kb0 + len && ok; ++kb, ++i) {
+                    const int s = i % kStagesG;
+                    ok = mbar_wait(bar(EMPTY + s), ((uint32_t)(i / kStagesG) & 1u) ^ 1u, prm.status);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(FULL_B + s), kBTileBytes);
+                    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(b_tiles + s * kBTileBytes);
+                    tma_load_2d(dst, &xmap, kb * kGroup, m0, bar(FULL_B + s));
+                    tma_load_2d(dst + NT * 128, &xmap, kb * kGroup + 64, m0, bar(FULL_B + s));
+                }
+                it += len;
+            } while (PERSIST && it < it_end && ok);
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             // instruction descriptor: FP32 accumulate, FP16 A and B, both K-major, M = 128, N = NT
             const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(kTileW >> 4) << 24);
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % kStagesG;
-                const uint32_t ph = (uint32_t)(i / kStagesG) & 1u;
-                ok = mbar_wait(bar(FULL_A + s), ph, prm.status) && mbar_wait(bar(FULL_B + s), ph, prm.status);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_tmem = tmem_base + (uint32_t)(kAccCols + s * kAStageCols);
-                const uint32_t b_addr = (uint32_t)__cvta_generic_to_shared(b_tiles + s * kBTileBytes);
+            int i = 0, seg = 0, it = it_begin;
+            do {
+                const int tile = it / groups, kb0 = it - tile * groups;
+                const int len = min(groups - kb0, it_end - it);
+                // the previous segment's accumulator must have been read out
+                if (PERSIST && seg > 0) ok = mbar_wait(bar(ACC_FREE), (uint32_t)(seg - 1) & 1u, prm.status);
+                for (int ii = 0; ii < len && ok; ++ii, ++i) {
+                    const int s = i % kStagesG;
+                    const uint32_t ph = (uint32_t)(i / kStagesG) & 1u;
+                    ok = mbar_wait(bar(FULL_A + s), ph, prm.status) && mbar_wait(bar(FULL_B + s), ph, prm.status);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_tmem = tmem_base + (uint32_t)(kAccCols + s * kAStageCols);
+                    const uint32_t b_addr = (uint32_t)__cvta_generic_to_shared(b_tiles + s * kBTileBytes);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {           // eight K = 16 steps; B: two 64-wide swizzle atoms
-                    const uint64_t db = umma_desc(b_addr + (j >> 2) * (NT * 128) + (j & 3) * 32);
-                    umma_f16_ts(tmem_base, a_tmem + 8u * j, db, idesc, (i > 0 || j > 0) ? 1u : 0u);
+                    for (int j = 0; j < 8; ++j) {           // eight K = 16 steps; B: two 64-wide swizzle atoms
+                        const uint64_t db = umma_desc(b_addr + (j >> 2) * (NT * 128) + (j & 3) * 32);
+                        umma_f16_ts(tmem_base, a_tmem + 8u * j, db, idesc, (ii > 0 || j > 0) ? 1u : 0u);
+                    }
+                    umma_commit(bar(EMPTY + s));            // the stage is free once these MMAs have read it
                 }
-                umma_commit(bar(EMPTY + s));            // the stage is free once these MMAs have read it
-            }
-            if (ok) umma_commit(bar(ACCUM));
+                if (ok) umma_commit(bar(ACCUM));            // the segment's accumulator is complete
+                it += len;
+                ++seg;
+            } while (PERSIST && it < it_end && ok);
         }
     } else {
         // ------------------------------------------------------------------ decode (thread = weight row)
@@ -297,15 +343,20 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         const int r = (warp & 3) * 32 + lane;            // 0..127 = tensor-memory lane (a warp reaches lanes 32*(warp%4)..)
         ok = mbar_wait(bar(LUT_BAR), 0, prm.status);
         const uint32_t lut_lane = (uint32_t)__cvta_generic_to_shared(lut) + (uint32_t)lane * 8u;
-        int pack_i = -1;
-        for (int i = 0; i < n_kb && ok; ++i) {
-            const int kb = kb_begin + i;
-            if (i == 0 || (kb % kPackGroups) == 0) {
+        int pack_i = -1, i = 0, seg = 0, it = it_begin;
+        do {
+        const int tile = it / groups, kb0 = it - tile * groups;
+        const int len = min(groups - kb0, it_end - it);
+        const int n0 = (tile / prm.tiles_m) * kTileW;       // first weight row of the tile
+        const int m0 = (tile % prm.tiles_m) * NT;           // first activation row
+        for (int ii = 0; ii < len && ok; ++ii, ++i) {
+            const int kb = kb0 + ii;
+            if (ii == 0 || (kb % kPackGroups) == 0) {
                 ++pack_i;
                 ok = mbar_wait(bar(PACK_FULL + pack_i % kPackBufs), (uint32_t)(pack_i / kPackBufs) & 1u, prm.status);
                 if (!ok) break;
             }
-            const bool last_of_chunk = (kb % kPackGroups) == kPackGroups - 1 || i == n_kb - 1;
+            const bool last_of_chunk = (kb % kPackGroups) == kPackGroups - 1 || ii == len - 1;
             if ((i & 1) != group) {                      // the other group's K block
                 if (last_of_chunk) mbar_arrive(bar(PACK_EMPTY + pack_i % kPackBufs));
                 continue;
@@ -369,10 +420,14 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             if (last_of_chunk) mbar_arrive(bar(PACK_EMPTY + pack_i % kPackBufs));
         }
 
-        // ------------------------------------------------------------------ epilogue (TMEM lane = weight row)
-        if (ok && group == 0) ok = mbar_wait(bar(ACCUM), 0, prm.status);
+        // ---------------------------------------------------------------- epilogue (TMEM lane = weight row)
+        // A segment that covers the tile's whole K range is stored as the result; a partial one goes to
+        // this CTA's first- or last-segment slot as FP32 and is added up by the fix-up kernel.
+        if (ok && group == 0) ok = mbar_wait(bar(ACCUM), (uint32_t)seg & 1u, prm.status);
         if (ok && group == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool whole = len == groups;
+            float *slot = prm.partials + ((size_t)2 * blockIdx.x + (seg == 0 ? 0 : 1)) * (size_t)(NT * kTileW);
             const int n = n0 + r;
 #pragma unroll 1
             for (int c0 = 0; c0 < NT; c0 += 32) {
@@ -386,8 +441,8 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     const int m = m0 + c0 + c;
                     if (c0 + c < NT && m < prm.M && n < prm.N) {
                         const float f = __uint_as_float(v[c]);
-                        if (prm.splits > 1)
-                            prm.partials[((size_t)blockIdx.z * prm.M + m) * prm.N + n] = f;
+                        if (!whole)
+                            slot[(c0 + c) * kTileW + r] = f;
                         else if (prm.y_f32)
                             static_cast<float *>(prm.y)[(size_t)m * prm.N + n] = f;
                         else
@@ -395,7 +450,13 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     }
                 }
             }
+            // the accumulator columns may be overwritten by the next segment
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(bar(ACC_FREE));
         }
+        it += len;
+        ++seg;
+        } while (PERSIST && it < it_end && ok);   // segments
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -414,15 +475,57 @@ __global__ void tq1_permute_x_kernel(const __half *__restrict__ x, __half *__res
     xp[i] = x[i - p + perm_column(p)];
 }
 
-// y[m][n] = sum over splits in ascending order.
-__global__ void tq1_splitk_reduce_kernel(const float *__restrict__ partials, void *__restrict__ y, int y_f32,
-                                         long long mn, int splits) {
-    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-    if (i >= mn) return;
-    float total = 0.0f;
-    for (int s = 0; s < splits; ++s) total += partials[(size_t)s * mn + i];
-    if (y_f32) static_cast<float *>(y)[i] = total;
-    else static_cast<__half *>(y)[i] = __float2half_rn(total);
+// Fix-up for output tiles whose K range was shared by several CTAs: adds their FP32 partial tiles in
+// ascending K order (CTA order), so the result does not depend on timing. blockIdx.x + 1 names a boundary
+// between two CTAs' ranges; the block of the first boundary inside a tile handles that tile (eight token
+// columns per block in blockIdx.y, one thread per weight row). Tiles computed by one CTA were stored directly.
+constexpr int kFixCols = 4;
+__global__ void __launch_bounds__(kTileW)
+tq1_streamk_fixup_kernel(const float *__restrict__ partials, void *__restrict__ y, int y_f32,
+                         int M, int N, int tiles_m, const WorkSplit work, int nt) {
+    const int groups = work.groups, ctas = work.ctas;
+    int c_lo, c_hi, tile, it0;
+    if (work.splits > 0) {                       // every tile in equal parts: blockIdx.x names the tile
+        tile = blockIdx.x;
+        c_lo = tile * work.splits;
+        c_hi = c_lo + work.splits - 1;
+        it0 = tile * groups;
+    } else {
+        c_lo = blockIdx.x;                                             // the CTA before the boundary
+        const int it_b = work.first_iter(c_lo + 1);
+        if (it_b % groups == 0) return;                                // the boundary falls between two tiles
+        tile = it_b / groups;
+        it0 = tile * groups;
+        if (work.first_iter(c_lo) > it0) return;                       // an earlier boundary lies in this tile
+        c_hi = c_lo + 1;
+        while (c_hi + 1 < ctas && work.first_iter(c_hi + 1) < it0 + groups) ++c_hi;
+    }
+    const int r = threadIdx.x;
+    const int n = (tile / tiles_m) * kTileW + r;
+    const int m0 = (tile % tiles_m) * nt;
+    const int c0 = blockIdx.y * kFixCols;
+    if (n >= N) return;
+    float total[kFixCols];
+#pragma unroll
+    for (int c = 0; c < kFixCols; ++c) total[c] = 0.0f;
+    for (int cta = c_lo; cta <= c_hi; ++cta) {
+        // the tile is that CTA's first segment if its range starts inside the tile, else its last one
+        const int which = work.splits > 0 || work.first_iter(cta) >= it0 ? 0 : 1;
+        const float *slot = partials + ((size_t)2 * cta + which) * (size_t)(nt * kTileW) + (size_t)c0 * kTileW + r;
+        float v[kFixCols];
+#pragma unroll
+        for (int c = 0; c < kFixCols; ++c) v[c] = m0 + c0 + c < M ? slot[c * kTileW] : 0.0f;
+#pragma unroll
+        for (int c = 0; c < kFixCols; ++c) total[c] += v[c];
+    }
+#pragma unroll
+    for (int c = 0; c < kFixCols; ++c) {
+        if (m0 + c0 + c < M) {
+            const size_t o = (size_t)(m0 + c0 + c) * N + n;
+            if (y_f32) static_cast<float *>(y)[o] = total[c];
+            else static_cast<__half *>(y)[o] = __float2half_rn(total[c]);
+        }
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -445,20 +548,37 @@ EncodeTiledFn gemm_encode_fn() {
 
 int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M < 1024 ? 128 : 256; }
 
-int pick_splits(int M, int N, int K) {
+// CTAs of a launch: every resident slot (two per SM for the 16-token tiles). With at least as many
+// tiles as slots the iterations are dealt out stream-K fashion; with fewer, every tile is cut into
+// equal parts of at least eight K blocks.
+WorkSplit pick_work(int M, int N, int K) {
     const int nt = token_tile(M);
     const long long tiles = (long long)((N + kTileW - 1) / kTileW) * ((M + nt - 1) / nt);
-    const int groups = K / kGroup;
-    int splits = 1;
-    const long long slots = nt <= 16 ? 296 : 148;            // CTAs resident at once
-    if (tiles < slots) {
-        splits = (int)(slots / tiles);
-        if (splits < 1) splits = 1;
-        const int max_splits = groups / 8 > 0 ? groups / 8 : 1;      // at least 8 groups per split
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+            sm_count = 148;
+    }
+    const long long slots = (long long)sm_count * (nt <= 16 ? 2 : 1);
+    WorkSplit w;
+    w.groups = K / kGroup;
+    w.total_iters = (int)(tiles * w.groups);
+    if (tiles >= slots) {
+        w.splits = 0;
+        w.ctas = (int)slots;
+    } else {
+        int splits = (int)(slots / tiles);
+        const int max_splits = w.groups / 8 > 0 ? w.groups / 8 : 1;
         if (splits > max_splits) splits = max_splits;
         if (splits > 32) splits = 32;
+        w.splits = splits;
+        w.ctas = (int)tiles * splits;
     }
-    return splits;
+    w.quot = w.total_iters / w.ctas;
+    w.rem = w.total_iters % w.ctas;
+    return w;
 }
 
 size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -469,9 +589,9 @@ size_t gemm_smem_bytes() {
            (size_t)gemm_pack_bufs(NT) * kPackBytes + kLutBytesG + 512 + 1024;
 }
 
-template <int NT>
+template <int NT, bool PERSIST>
 int launch_nt(const CUtensorMap &wmap, const CUtensorMap &xmap, const GemmParams &prm, dim3 grid, cudaStream_t stream) {
-    auto kern = tq1_gemm_tc_kernel<NT>;
+    auto kern = tq1_gemm_tc_kernel<NT, PERSIST>;
     static bool attr_set = false;
     const size_t smem = gemm_smem_bytes<NT>();
     if (!attr_set) {
@@ -497,10 +617,8 @@ bool gemm_tc_supported(const uint8_t *blocks, const __half *x, int M, int N, int
 }
 
 size_t gemm_tc_workspace_bytes(int M, int N, int K) {
-    const int splits = pick_splits(M, N, K);
-    size_t bytes = kWsScratchOffset + align256((size_t)M * K * sizeof(__half));
-    if (splits > 1) bytes += align256((size_t)splits * M * N * sizeof(float));
-    return bytes;
+    const size_t slots = (size_t)2 * pick_work(M, N, K).ctas * token_tile(M) * kTileW * sizeof(float);
+    return kWsScratchOffset + align256((size_t)M * K * sizeof(__half)) + align256(slots);
 }
 
 int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int M, int N, int K,
@@ -512,7 +630,8 @@ int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, 
     __half *xperm = reinterpret_cast<__half *>(ws + kWsScratchOffset);
     float *partials = reinterpret_cast<float *>(ws + kWsScratchOffset + align256((size_t)M * K * sizeof(__half)));
     const int nt = token_tile(M);
-    const int splits = pick_splits(M, N, K);
+    const WorkSplit work = pick_work(M, N, K);
+    const int ctas = work.ctas;
 
     const long long total = (long long)M * K;
     tq1_permute_x_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, xperm, total);
@@ -550,20 +669,32 @@ int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, 
     prm.M = M;
     prm.N = N;
     prm.K = K;
-    prm.splits = splits;
+    prm.tiles_m = (M + nt - 1) / nt;
+    prm.work = work;
     prm.y_f32 = y_f32 ? 1 : 0;
-    dim3 grid((unsigned)((N + kTileW - 1) / kTileW), (unsigned)((M + nt - 1) / nt), (unsigned)splits);
-    int rc = nt == 16 ? launch_nt<16>(wmap, xmap, prm, grid, stream)
-           : nt == 32 ? launch_nt<32>(wmap, xmap, prm, grid, stream)
-           : nt == 64 ? launch_nt<64>(wmap, xmap, prm, grid, stream)
-           : nt == 128 ? launch_nt<128>(wmap, xmap, prm, grid, stream)
-                       : launch_nt<256>(wmap, xmap, prm, grid, stream);
+    dim3 grid((unsigned)ctas);
+    int rc;
+    if (work.splits > 0)        // one segment per CTA
+        rc = nt == 16 ? launch_nt<16, false>(wmap, xmap, prm, grid, stream)
+           : nt == 32 ? launch_nt<32, false>(wmap, xmap, prm, grid, stream)
+           : nt == 64 ? launch_nt<64, false>(wmap, xmap, prm, grid, stream)
+           : nt == 128 ? launch_nt<128, false>(wmap, xmap, prm, grid, stream)
+                       : launch_nt<256, false>(wmap, xmap, prm, grid, stream);
+    else
+        rc = nt == 16 ? launch_nt<16, true>(wmap, xmap, prm, grid, stream)
+           : nt == 32 ? launch_nt<32, true>(wmap, xmap, prm, grid, stream)
+           : nt == 64 ? launch_nt<64, true>(wmap, xmap, prm, grid, stream)
+           : nt == 128 ? launch_nt<128, true>(wmap, xmap, prm, grid, stream)
+                       : launch_nt<256, true>(wmap, xmap, prm, grid, stream);
     if (rc != TQ1_OK) return rc;
-    if (splits > 1) {
-        const long long mn = (long long)M * N;
-        tq1_splitk_reduce_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, stream>>>(partials, y, prm.y_f32, mn, splits);
+    const bool shared_tiles = work.splits > 1 || (work.splits == 0 && (work.rem != 0 || work.quot % work.groups != 0));
+    if (ctas > 1 && shared_tiles) {
+        const unsigned fix_blocks = work.splits > 0 ? (unsigned)(ctas / work.splits) : (unsigned)(ctas - 1);
+        const unsigned col_blocks = (unsigned)(((M < nt ? M : nt) + kFixCols - 1) / kFixCols);
+        tq1_streamk_fixup_kernel<<<dim3(fix_blocks, col_blocks), kTileW, 0, stream>>>(
+            partials, y, prm.y_f32, M, N, prm.tiles_m, work, nt);
         err = cudaGetLastError();
-        if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: split-K reduce launch");
+        if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: stream-K fix-up launch");
     }
     return TQ1_OK;
 }

@@ -83,7 +83,7 @@ class LayerStack:
 
     def __init__(self, *, layers: int, batch: int = 1, shape: LayerShape = LayerShape(),
                  vocab: int = 0, rank: int = 0, world: int = 1, device=None, seed: int = 0,
-                 group=None, fused: bool = False, exchange: str = "p2p") -> None:
+                 group=None, fused: bool = False, exchange: str = "p2p", weights_from: "LayerStack | None" = None) -> None:
         self.layers, self.batch, self.shape = layers, batch, shape
         self.rank, self.world, self.group = rank, world, group
         self.device = torch.device(device if device is not None else "cuda")
@@ -96,8 +96,13 @@ class LayerStack:
             if n % world or (n // world) % 16:
                 raise ValueError(f"{n} output rows do not shard evenly over {world} ranks")
         # weights[l][j]: this rank's rows [rank*N/P, (rank+1)*N/P) of projection j in layer l
-        self.weights = [[random_blocks_device(n // world, k, gen, self.device) for _, n, k in self.projections]
-                        for _ in range(layers)]
+        if weights_from is not None:       # a second stack (another batch size) over the same resident weights
+            if (weights_from.projections, weights_from.world, weights_from.layers) != (self.projections, world, layers):
+                raise ValueError("weights_from must have the same layers, projections and sharding")
+            self.weights = weights_from.weights
+        else:
+            self.weights = [[random_blocks_device(n // world, k, gen, self.device) for _, n, k in self.projections]
+                            for _ in range(layers)]
         xg = torch.Generator(device=self.device)
         xg.manual_seed(seed + 7)   # same activations on every rank
         self.inputs = {k: torch.randn((batch, k), generator=xg, device=self.device).to(torch.float16)
@@ -109,7 +114,8 @@ class LayerStack:
                         for n in sorted({n for _, n, _ in self.projections})}
         self.vocab = vocab
         if vocab:
-            self.table = random_blocks_device(vocab, shape.hidden, gen, self.device)
+            self.table = (weights_from.table if weights_from is not None and weights_from.vocab == vocab
+                          else random_blocks_device(vocab, shape.hidden, gen, self.device))
             self.ids = torch.randint(0, vocab, (batch,), generator=xg, device=self.device)
             self.embedded = torch.zeros((batch, shape.hidden), dtype=torch.float16, device=self.device)
         ws_bytes = max(self.lib.tq1_linear_workspace_bytes(batch, n // world, k) for _, n, k in self.projections)
