@@ -21,6 +21,9 @@ def __getattr__(name):
     if name in ("PackedLinear", "PackedEmbedding", "packed_matmul"):
         from . import modules
         return getattr(modules, name)
+    if name in ("replace_with_packed", "expect_counts", "blocks_from_ternary"):
+        from . import packed_model
+        return getattr(packed_model, name)
     if name in ("tq1_matmul", "tq1_gemm", "tq1_get_rows", "validate_device_blocks"):
         from . import ops
         return getattr(ops, name)

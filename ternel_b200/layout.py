@@ -155,3 +155,36 @@ def unpack_blocks(codes: np.ndarray, scales: np.ndarray, *, layout: PackedTensor
     check(_native.lib().tq1_untile_blocks(_ptr(code_array), _ptr(scale_array), _ptr(blocks),
                                           layout.rows, layout.groups_per_row, layout.tile))
     return blocks
+
+
+@dataclass(frozen=True)
+class ModelLinearShape:
+    """One distinct linear weight shape of the 27B model and how many matmuls of that shape a
+    decoded token issues (src/ternel_mlx/layout.py:150-198)."""
+
+    label: str
+    rows: int
+    columns: int
+    dispatches_per_token: int
+
+    def layout(self) -> PackedTensorLayout:
+        return PackedTensorLayout.for_tensor(self.rows, self.columns)
+
+
+# 48 linear-attention layers of eight matmuls, 16 full-attention layers of seven, one output head.
+# Shapes outside the four benchmark shapes matter for coverage: 48 rows (not a multiple of 128 or of
+# the 256-row tile), K = 6144, and a 248,320-row head.
+MODEL_LINEAR_SHAPES: tuple[ModelLinearShape, ...] = (
+    ModelLinearShape("linear_attn.in_proj_a/b", 48, 5120, 96),
+    ModelLinearShape("self_attn.k_proj/v_proj", 1024, 5120, 32),
+    ModelLinearShape("linear_attn.out_proj, self_attn.o_proj", 5120, 6144, 64),
+    ModelLinearShape("mlp.down_proj", 5120, 17408, 64),
+    ModelLinearShape("linear_attn.in_proj_z", 6144, 5120, 48),
+    ModelLinearShape("linear_attn.in_proj_qkv", 10240, 5120, 48),
+    ModelLinearShape("self_attn.q_proj", 12288, 5120, 16),
+    ModelLinearShape("mlp.gate_proj/up_proj", 17408, 5120, 128),
+    ModelLinearShape("lm_head", 248320, 5120, 1),
+)
+DISPATCHES_PER_TOKEN = 497
+if sum(shape.dispatches_per_token for shape in MODEL_LINEAR_SHAPES) != DISPATCHES_PER_TOKEN:
+    raise FormatError("the shape census no longer accounts for a whole decoded token")

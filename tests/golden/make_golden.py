@@ -51,11 +51,57 @@ def _random_case(fmt, rows, columns, seed, *, dist):
     return trits, scales, blocks.reshape(rows, columns // 128, 28), rng
 
 
+def _write_sidecars(fmt, reorder) -> None:
+    """A two-tensor ``.tq1g128`` file assembled with the reference's header and manifest code the way
+    its packer does, and the LUT23 container its ``reorder_sidecar`` makes from it."""
+    import json
+
+    tensors = []
+    for name, rows, columns, seed in (("blk.0.ffn_down.weight", 300, 256, 21), ("blk.0.ssm_a.weight", 48, 128, 22)):
+        _, _, blocks, _ = _random_case(fmt, rows, columns, seed, dist="tests")
+        tensors.append((name, rows, columns, blocks))
+    path = HERE / "sidecar_small.tq1g128"
+    entries = []
+    with path.open("wb") as handle:
+        handle.write(bytes(fmt.HEADER_BYTES))
+        for index, (name, rows, columns, blocks) in enumerate(tensors):
+            offset = fmt.align_up(handle.tell(), fmt.ALIGNMENT)
+            fmt.write_padding(handle, offset)
+            data = blocks.tobytes()
+            handle.write(data)
+            entries.append({
+                "index": index, "name": name, "shape_gguf": [columns, rows], "elements": rows * columns,
+                "groups": rows * columns // 128, "source_type": "Q2_0", "source_offset": 0, "source_bytes": 0,
+                "packed_offset": offset, "packed_bytes": len(data),
+                "logical_weight_sha256": "11" * 32, "scale_bits_sha256": "22" * 32,
+                "packed_payload_sha256": hashlib.sha256(data).hexdigest(),
+            })
+        manifest_offset = handle.tell()
+        manifest = {"format": "TQ1_G128", "version": fmt.VERSION, "block_size": 128, "block_bytes": 28,
+                    "alignment": fmt.ALIGNMENT, "mapping": {"-1": 0, "0": 1, "+1": 2},
+                    "packed_payload_bytes": sum(e["packed_bytes"] for e in entries), "tensors": entries}
+        raw = fmt.canonical_json_bytes(manifest)
+        handle.write(raw)
+        header = fmt.SidecarHeader(version=fmt.VERSION, header_bytes=fmt.HEADER_BYTES, block_size=128, block_bytes=28,
+                                   alignment=fmt.ALIGNMENT, tensor_count=len(entries), source_file_bytes=4242,
+                                   manifest_offset=manifest_offset, manifest_bytes=len(raw), source_sha256="ab" * 32)
+        handle.seek(0)
+        handle.write(header.pack())
+    fmt.read_sidecar(path)                                   # the reference's own reader accepts it
+    reorder.reorder_sidecar(path, HERE / "sidecar_small.lut23")
+    np.savez_compressed(HERE / "sidecar_small_blocks.npz", **{name: blocks for name, _, _, blocks in tensors})
+    print("wrote sidecar_small.tq1g128, sidecar_small.lut23, sidecar_small_blocks.npz")
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference", type=Path, required=True)
+    parser.add_argument("--sidecars-only", action="store_true", help="write only the two sidecar fixtures")
     args = parser.parse_args()
     fmt, ref, reorder, layout, packing, mref = _import_reference(args.reference)
+    _write_sidecars(fmt, reorder)
+    if args.sidecars_only:
+        return
 
     # 1. codec: every legal byte value in slot 0 and the tail, odd scale bit patterns.
     codes = np.ones((243, 128), dtype=np.uint8)
