@@ -117,20 +117,26 @@ int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
 
 /* One rank's view of an output-row shard. Output rows are independent, so rank r owns rows
  * [n_offset, n_offset + N_local) of a projection and the FP16 results are written straight
- * into every rank's gathered activation buffer (peer mappings over NVLink), then a flag is
- * raised on every rank. The reference has no multi-device path (its CUDA branch states
- * "currently supports one CUDA device", patches/prism-tq1-g128-distribution.patch:373). */
+ * into every rank's gathered activation buffer (peer mappings over NVLink). Flags are per tile
+ * of 16 rows: after a tile has been written to a rank, word (row / 16) of that rank's flag array
+ * for the buffer is set to the publish epoch with a release store. A consumer waits until the
+ * flags of the tiles it reads have reached its wait epoch. The reference has no multi-device
+ * path (its CUDA branch states "currently supports one CUDA device",
+ * patches/prism-tq1-g128-distribution.patch:373). */
 typedef struct tq1_shard {
     int rank, world;            /* world <= 8 */
     int n_offset;               /* first gathered row of this shard, a multiple of 16 */
     int n_total;                /* rows of the gathered output */
     void *peer_y[8];            /* device pointers: rank p's gathered output, FP16 [M][n_total] */
-    uint32_t *peer_flags[8];    /* device pointers: rank p's flag words (>= world); word s is written by rank s */
+    uint32_t *peer_flags[8];    /* device pointers: rank p's tile flags of that output, n_total / 16 words */
     const uint32_t *epoch_base; /* optional device word added to both epochs below (NULL: 0); lets a
                                    captured CUDA graph publish fresh epochs on every replay */
-    uint32_t publish_epoch;     /* written to word `rank` of every rank's flags when the shard is complete */
-    const uint32_t *wait_flags; /* local flag words to wait on before x is read (NULL: do not wait) */
-    uint32_t wait_epoch;        /* wait until every word has reached this value */
+    uint32_t publish_epoch;     /* stored to a tile's flag on every rank once the tile is there */
+    const uint32_t *wait_flags; /* local tile flags of the buffer x lives in (NULL: do not wait); flag t
+                                   guards x[..][16t .. 16t+15] */
+    uint32_t wait_epoch;        /* wait until the flags have reached this value */
+    int wait_tiles;             /* number of words behind wait_flags; M == 1 waits only for the tiles a
+                                   CTA reads, M >= 2 for all of them */
 } tq1_shard;
 
 size_t tq1_linear_sharded_workspace_bytes(int M, int N_local, int K);
@@ -138,9 +144,9 @@ size_t tq1_linear_sharded_workspace_bytes(int M, int N_local, int K);
 /* *epoch_base += delta on the stream (one per decode step, before its first sharded call). */
 int tq1_shard_advance_epoch(uint32_t *epoch_base, uint32_t delta, void *stream);
 
-/* blocks: this rank's rows [N_local][K/128][28]; x: the whole FP16 activations [M][K] in local
- * memory. Waits are bounded: if a flag never arrives the status word at the start of the
- * workspace becomes 4 and the call completes with whatever was there. */
+/* blocks: this rank's rows [N_local][K/128][28] (N_local a multiple of 16); x: the whole FP16
+ * activations [M][K] in local memory. Waits are bounded: if a flag never arrives the status word
+ * at the start of the workspace becomes 4 and the call completes with whatever was there. */
 int tq1_linear_f16_sharded(const uint8_t *blocks, const void *x, const tq1_shard *shard,
                            int M, int N_local, int K, void *workspace, size_t workspace_bytes, void *stream);
 

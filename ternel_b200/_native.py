@@ -47,7 +47,7 @@ class Shard(ctypes.Structure):
         ("rank", c_int), ("world", c_int), ("n_offset", c_int), ("n_total", c_int),
         ("peer_y", c_void_p * 8), ("peer_flags", c_void_p * 8),
         ("epoch_base", c_void_p), ("publish_epoch", ctypes.c_uint32), ("wait_flags", c_void_p),
-        ("wait_epoch", ctypes.c_uint32),
+        ("wait_epoch", ctypes.c_uint32), ("wait_tiles", c_int),
     ]
 
 

@@ -63,6 +63,11 @@ int tq1_linear_f16_sharded(const uint8_t *blocks, const void *x, const tq1_shard
     if (M <= 0) return fail(TQ1_ERR_INVALID, "activations have an empty batch dimension");
     if (N_local <= 0 || K <= 0 || K % kGroup)
         return fail(TQ1_ERR_INVALID, "tq1_linear_f16_sharded: bad shard shape %dx%d", N_local, K);
+    if (N_local % kFlagRows)
+        return fail(TQ1_ERR_INVALID, "tq1_linear_f16_sharded: a shard of %d rows is not a multiple of %d", N_local,
+                    kFlagRows);
+    if (shard->wait_flags && shard->wait_tiles < 0)
+        return fail(TQ1_ERR_INVALID, "tq1_linear_f16_sharded: negative wait_tiles");
     if (shard->n_offset < 0 || shard->n_offset % 16 || shard->n_offset + N_local > shard->n_total)
         return fail(TQ1_ERR_INVALID, "tq1_linear_f16_sharded: rows [%d, %d) do not fit %d gathered rows "
                     "(the offset must be a multiple of 16)", shard->n_offset, shard->n_offset + N_local, shard->n_total);
@@ -76,15 +81,15 @@ int tq1_linear_f16_sharded(const uint8_t *blocks, const void *x, const tq1_shard
         if (!shard->peer_y[p] || !shard->peer_flags[p])
             return fail(TQ1_ERR_INVALID, "tq1_linear_f16_sharded: missing peer pointer for rank %d", p);
         sd.peer_y[p] = static_cast<__half *>(shard->peer_y[p]) + shard->n_offset;
-        sd.peer_flags[p] = shard->peer_flags[p];
+        sd.peer_flags[p] = shard->peer_flags[p] + shard->n_offset / kFlagRows;
     }
     sd.epoch_base = shard->epoch_base;
     sd.publish_epoch = shard->publish_epoch;
     sd.wait_flags = shard->wait_flags;
+    sd.wait_tiles = shard->wait_flags ? shard->wait_tiles : 0;
     sd.wait_epoch = shard->wait_epoch;
     sd.ld_total = shard->n_total;
     unsigned *status = static_cast<unsigned *>(workspace);
-    sd.done_counter = status + 1;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (M == 1 && gemv_stream_supported(blocks, N_local, K))     // the GEMV's epilogue does the push itself
         return launch_gemv_stream(blocks, static_cast<const __half *>(x), nullptr, false, N_local, K, workspace, s, &sd);

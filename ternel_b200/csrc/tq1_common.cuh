@@ -37,17 +37,20 @@ int launch_gemv_rows(const uint8_t *blocks, const __half *x, void *y, bool y_f32
 
 // Device-side description of an output-row shard whose result is pushed to every rank
 // (tq1_linear_f16_sharded): peer pointers are plain device addresses reachable over NVLink.
+// Flags are per row tile: word t of a gathered buffer's flag array guards rows [16t, 16t + 16) and is
+// stored, with release semantics, by the thread that has just written those rows to that rank.
 constexpr int kMaxRanks = 8;
+constexpr int kFlagRows = 16;
 struct ShardDev {
     int world;                          // <= 1: not sharded, every other field is ignored
     int rank;
     __half *peer_y[kMaxRanks];          // rank p's gathered output, already advanced to this shard's first row
-    unsigned *peer_flags[kMaxRanks];    // rank p's flag words; word `rank` is ours to write
+    unsigned *peer_flags[kMaxRanks];    // rank p's tile flags of that output, advanced to this shard's first tile
     const unsigned *epoch_base;         // optional device word added to both epochs (graph replays advance it)
-    unsigned publish_epoch;             // value published once the whole shard has been written everywhere
-    const unsigned *wait_flags;         // local flag words to wait on before activations are read (or null)
+    unsigned publish_epoch;             // value stored to a tile's flag once the tile has been written
+    const unsigned *wait_flags;         // local tile flags of the activations this call reads (or null)
+    int wait_tiles;                     // how many of them exist
     unsigned wait_epoch;
-    unsigned *done_counter;             // device word, zero between calls
     int ld_total;                       // row length of the gathered output (elements)
 };
 

@@ -320,13 +320,16 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (shard.world > 1 && shard.wait_flags != nullptr) {
-        // Row-sharded input: every rank's piece of the activations must have landed in local memory.
-        if (tid < shard.world) {
+        // Row-sharded input: the tiles of activations this CTA reads (32 per chunk) must have landed
+        // in local memory from whichever rank computed them.
+        const int cl = tid >> 5;
+        const int tile = (chunk_lo + cl) * (kChunkGroups * kGroup / kFlagRows) + lane;
+        if (cl < kMaxChunksPerCta && chunk_lo + cl <= chunk_hi && tile < shard.wait_tiles) {
             const unsigned want = shard.wait_epoch + (shard.epoch_base ? *shard.epoch_base : 0u);
             uint32_t spins = 0;
             for (;;) {
                 unsigned v;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(shard.wait_flags + tid) : "memory");
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(shard.wait_flags + tile) : "memory");
                 if ((int)(v - want) >= 0) break;
                 if (++spins > kMaxWaitSpins) { atomicExch(status, 4u); break; }   // never hang
             }
@@ -558,14 +561,12 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
     // for warps that are running. Lane (hf, r) adds chunks hf, hf+2, ... of row r in ascending order
     // and one shuffle joins the two halves: the order of additions never depends on timing.
     PHASE(7);
-    int tiles_finished = 0;
     {
         const int r = lane & 15, hf = lane >> 4;
         const size_t stride = (size_t)tiles * kTileRows;
         int cc = c_first, tt = t_first;
         for (int i = 0; i < n_units; ++i) {
             if (tt % chunks == cc) {                 // warp-uniform: this warp owns row tile tt
-                ++tiles_finished;
                 unsigned long long *p = slots + (size_t)tt * kTileRows + r;
                 float total = 0.0f;
                 for (int c0 = hf; c0 < chunks; c0 += 16) {
@@ -588,34 +589,29 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
                 }
                 total += __shfl_xor_sync(0xffffffffu, total, 16);
                 const int row = tt * kTileRows + r;
-                if (hf == 0 && row < N) {
-                    if (shard.world > 1) {
-                        // fused all-gather: the finished rows go straight into every rank's gathered output
-                        for (int p2 = 0; p2 < shard.world; ++p2) shard.peer_y[p2][row] = __float2half_rn(total);
-                    } else if (OUT_F32) {
-                        static_cast<float *>(y)[row] = total;
-                    } else {
-                        static_cast<__half *>(y)[row] = __float2half_rn(total);
+                if (shard.world > 1) {
+                    // Fused all-gather: lane p sends the tile's 16 FP16 rows (two 16-byte stores) into
+                    // rank p's gathered output and then raises the tile's flag there; the release store
+                    // orders that lane's own data stores before the flag, so no fence or counter is needed.
+                    const uint32_t mine = (uint32_t)__half_as_ushort(__float2half_rn(total));
+                    const uint32_t pair = mine | ((uint32_t)__shfl_down_sync(0xffffffffu, mine, 1) << 16);
+                    uint32_t w[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) w[k] = __shfl_sync(0xffffffffu, pair, 2 * k);
+                    if (lane < shard.world) {
+                        uint4 *dst = reinterpret_cast<uint4 *>(shard.peer_y[lane] + (size_t)tt * kTileRows);
+                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        const unsigned epoch = shard.publish_epoch + (shard.epoch_base ? *shard.epoch_base : 0u);
+                        asm volatile("st.release.sys.global.u32 [%0], %1;"
+                                     ::"l"(shard.peer_flags[lane] + tt), "r"(epoch) : "memory");
                     }
+                } else if (hf == 0 && row < N) {
+                    if (OUT_F32) static_cast<float *>(y)[row] = total;
+                    else static_cast<__half *>(y)[row] = __float2half_rn(total);
                 }
             }
             if (++tt == tiles) { tt = 0; ++cc; }
-        }
-    }
-    if (shard.world > 1 && tiles_finished > 0) {
-        // Publish: once every row tile of the shard has been written to every rank, raise our flag there.
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) {
-            const unsigned before = atomicAdd(shard.done_counter, (unsigned)tiles_finished);
-            if (before + (unsigned)tiles_finished == (unsigned)tiles) {
-                atomicExch(shard.done_counter, 0u);
-                __threadfence_system();
-                const unsigned epoch = shard.publish_epoch + (shard.epoch_base ? *shard.epoch_base : 0u);
-                for (int p = 0; p < shard.world; ++p)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;"
-                                 ::"l"(shard.peer_flags[p] + shard.rank), "r"(epoch) : "memory");
-            }
         }
     }
     PHASE(8);
@@ -749,10 +745,7 @@ static int launch_gemv_rows_block(const uint8_t *blocks, const __half *x, void *
     cfg.numAttrs = use_pdl ? 1 : 0;
     const __half *xc = x;
     ShardDev sd = {};
-    if (shard) {
-        sd = *shard;
-        sd.done_counter = status + 1;       // second word of the workspace header, zero between calls
-    }
+    if (shard) sd = *shard;
     cudaError_t err =
         y_f32 ? cudaLaunchKernelEx(&cfg, kf, map, xc, y, N, K, tiles, chunks, slots, status, sd)
               : cudaLaunchKernelEx(&cfg, kh, map, xc, y, N, K, tiles, chunks, slots, status, sd);

@@ -81,8 +81,14 @@ class EpochClock:
 
 
 def make_shard(*, rank: int, plan: ShardPlan, peer_y: list[int], peer_flags: list[int], epoch_base: int,
-               publish_epoch: int, wait_epoch: int, wait: bool = True) -> _native.Shard:
-    """Fill a ``tq1_shard`` for one call. ``peer_y[p]`` / ``peer_flags[p]`` are device addresses on rank p."""
+               publish_epoch: int, wait_epoch: int, wait_flags: int | None = None,
+               wait_tiles: int | None = None) -> _native.Shard:
+    """Fill a ``tq1_shard`` for one call.
+
+    ``peer_y[p]`` / ``peer_flags[p]`` are device addresses on rank p of the gathered output and of its
+    tile flags (one 32-bit word per 16 rows). ``wait_flags`` is the local flag array of the buffer the
+    activations were gathered into (``wait_tiles`` words); ``None`` skips the wait.
+    """
     if len(peer_y) != plan.world or len(peer_flags) != plan.world:
         raise ValueError("one gathered buffer and one flag array per rank are required")
     first, _ = plan.rows(rank)
@@ -94,7 +100,8 @@ def make_shard(*, rank: int, plan: ShardPlan, peer_y: list[int], peer_flags: lis
         shard.peer_flags[p] = peer_flags[p]
     shard.epoch_base = epoch_base or None
     shard.publish_epoch = publish_epoch
-    shard.wait_flags = peer_flags[rank] if wait else None
+    shard.wait_flags = wait_flags or None
+    shard.wait_tiles = int(wait_tiles or 0) if wait_flags else 0
     shard.wait_epoch = wait_epoch
     return shard
 

@@ -133,10 +133,13 @@ class LayerStack:
         from .sharding import EpochClock, ShardPlan
 
         sizes = sorted({n for _, n, _ in self.projections})
-        self._offsets, cursor = {}, 1024               # [flags 256 B | epoch base 4 B | pad] then the buffers
+        # arena: [epoch base 4 B | pad to 1 KiB] then, per output size, the gathered buffer and its tile flags
+        self._offsets, self._flag_offsets, cursor = {}, {}, 1024
         for n in sizes:
             self._offsets[n] = cursor
             cursor += (self.batch * n * 2 + 255) // 256 * 256
+            self._flag_offsets[n] = cursor
+            cursor += (n // 16 * 4 + 255) // 256 * 256
         arena = symm_mem.empty(cursor, dtype=torch.uint8, device=self.device)
         arena.zero_()
         handle = symm_mem.rendezvous(arena, self.group if self.group is not None else dist.group.WORLD)
@@ -146,7 +149,7 @@ class LayerStack:
                         .view(self.batch, n) for n in sizes}
         self._plans = {n: ShardPlan(n, self.world) for n in sizes}
         self._clock = EpochClock()
-        self._epoch_base_ptr = self._peer_base[self.rank] + 256
+        self._epoch_base_ptr = self._peer_base[self.rank]
         ws_bytes = max(self.lib.tq1_linear_sharded_workspace_bytes(self.batch, n // self.world, k)
                        for _, n, k in self.projections)
         self.workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device=self.device)
@@ -198,17 +201,22 @@ class LayerStack:
         """Every projection pushes its rows into all ranks' gathered buffers; the next one waits for the flags."""
         from .sharding import make_shard, sharded_linear
         lib, world, rank = self.lib, self.world, self.rank
-        flags = [base for base in self._peer_base]
+        local = self._peer_base[rank]
+        prev_n = self.projections[-1][1]          # a step starts after the previous step's last projection
         for layer in self.weights:
             for (_, n, k), blocks in zip(self.projections, layer):
                 publish, wait = self._clock.next()
+                # the input stands for the previous projection's gathered output: wait for the tiles of
+                # that buffer which cover this projection's K columns
                 shard = make_shard(rank=rank, plan=self._plans[n],
                                    peer_y=[base + self._offsets[n] for base in self._peer_base],
-                                   peer_flags=flags, epoch_base=self._epoch_base_ptr,
-                                   publish_epoch=publish, wait_epoch=wait)
+                                   peer_flags=[base + self._flag_offsets[n] for base in self._peer_base],
+                                   epoch_base=self._epoch_base_ptr, publish_epoch=publish, wait_epoch=wait,
+                                   wait_flags=local + self._flag_offsets[prev_n], wait_tiles=min(k, prev_n) // 16)
                 sharded_linear(lib, blocks.data_ptr(), self.inputs[k].data_ptr(), shard, batch=self.batch,
                                n_local=n // world, columns=k, workspace_ptr=self.workspace.data_ptr(),
                                workspace_bytes=self.workspace_bytes, stream_ptr=stream)
+                prev_n = n
         check(lib.tq1_shard_advance_epoch(self._epoch_base_ptr, self._clock.reset(), stream))
 
     def checksum(self) -> float:

@@ -24,19 +24,18 @@ class TwoRanks:
         self.plan = ShardPlan(rows, 2)
         self.rows, self.columns, self.batch = rows, columns, batch
         self.y = [torch.zeros((batch, rows), dtype=torch.float16, device="cuda") for _ in range(2)]
-        self.flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2)]
+        self.flags = [torch.zeros(rows // 16, dtype=torch.int32, device="cuda") for _ in range(2)]   # one per row tile
         self.base = torch.zeros(1, dtype=torch.int32, device="cuda")
         need = self.lib.tq1_linear_sharded_workspace_bytes(batch, rows // 2, columns)
         self.ws = [torch.zeros(need, dtype=torch.uint8, device="cuda") for _ in range(2)]
 
-    def call(self, rank, blocks_dev, x_dev, publish, wait_epoch, wait=True, wait_flags=None):
+    def call(self, rank, blocks_dev, x_dev, publish, wait_epoch, wait=True):
         from ternel_b200 import _native
         from ternel_b200.sharding import make_shard
         shard = make_shard(rank=rank, plan=self.plan, peer_y=[t.data_ptr() for t in self.y],
                            peer_flags=[t.data_ptr() for t in self.flags], epoch_base=self.base.data_ptr(),
-                           publish_epoch=publish, wait_epoch=wait_epoch, wait=wait)
-        if wait_flags is not None:
-            shard.wait_flags = wait_flags
+                           publish_epoch=publish, wait_epoch=wait_epoch,
+                           wait_flags=self.flags[rank].data_ptr() if wait else None, wait_tiles=self.rows // 16)
         first, count = self.plan.rows(rank)
         rc = self.lib.tq1_linear_f16_sharded(
             blocks_dev[first:first + count].contiguous().data_ptr(), x_dev.data_ptr(), ctypes.byref(shard),
@@ -63,7 +62,7 @@ def test_shards_land_in_every_ranks_buffer(rows, columns, batch):
         for rank in range(2):
             got = ranks.y[rank].float().cpu().numpy()
             assert o.normalised_error(got, want) < 2e-3
-            assert ranks.flags[rank][:2].tolist() == [2 * step + 2, 2 * step + 2]
+            assert bool((ranks.flags[rank] == 2 * step + 2).all())          # every tile's flag, from both shards
             assert int(ranks.ws[rank][:8].view(torch.int32)[0]) == 0          # status word: no timeout
         assert torch.equal(ranks.y[0], ranks.y[1])
 

@@ -40,9 +40,13 @@ def test_epoch_clock_and_shard_struct():
     assert clock.reset() == 3 and clock.next() == (1, 0)
     plan = ShardPlan(1024, 2)
     shard = make_shard(rank=1, plan=plan, peer_y=[0x1000, 0x2000], peer_flags=[0x100, 0x200], epoch_base=0x300,
-                       publish_epoch=5, wait_epoch=4)
+                       publish_epoch=5, wait_epoch=4, wait_flags=0x200, wait_tiles=64)
     assert (shard.rank, shard.world, shard.n_offset, shard.n_total) == (1, 2, 512, 1024)
     assert shard.peer_y[1] == 0x2000 and shard.wait_flags == 0x200 and shard.epoch_base == 0x300
+    assert shard.wait_tiles == 64
+    nowait = make_shard(rank=0, plan=plan, peer_y=[1, 2], peer_flags=[3, 4], epoch_base=0, publish_epoch=1,
+                        wait_epoch=0)
+    assert not nowait.wait_flags and nowait.wait_tiles == 0
     with pytest.raises(ValueError, match="per rank"):
         make_shard(rank=0, plan=plan, peer_y=[1], peer_flags=[1, 2], epoch_base=0, publish_epoch=1, wait_epoch=0)
 
