@@ -20,8 +20,10 @@
 //              its A operand (the weights never pass through shared memory); the two groups take
 //              alternate K blocks. After a segment's K loop warps 0-3 read the accumulator (TMEM
 //              lane r = weight row r) and store it, then release it to the MMA warp
-//   warp 8     TMA: packed weight bytes (box 128 rows x 112 B = 4 groups) and activation tiles
-//   warp 9     allocates tensor memory and issues tcgen05.mma (one elected lane)
+//   one warp   TMA: packed weight bytes (box 128 rows x 112 B = 4 groups) and activation tiles
+//   one warp   allocates tensor memory and issues tcgen05.mma (one elected lane)
+//   warps 8-11 (persistent kernel, 32- to 128-token tiles only) read finished accumulators and store
+//              the results while the MMA warp fills a second accumulator with the next segment
 //
 // K order. Five trits per byte do not pair up in natural order, so inside every 128-wide
 // group the K axis is permuted to a decode-friendly order (position p -> column pi(p) below)
@@ -44,8 +46,12 @@ constexpr int kTileW = 128;                 // weight rows per tile (UMMA M)
 constexpr int kPackGroups = 4;
 constexpr int kPackBytes = kTileW * kPackGroups * kBlockBytes;     // 14336
 constexpr int kLutBytesG = 243 * 256;                              // 8-byte entries x 32 lanes
-constexpr int kGemmThreads = 320;            // warps 0-3 and 4-7 decode, warp 8 TMA, warp 9 MMA
-constexpr int kTmaWarp = 8, kMmaWarp = 9;
+// Warp roles. Plain variant (320 threads): warps 0-3 and 4-7 decode, warp 8 TMA, warp 9 MMA, and the first
+// decode group also stores the results. Variant with epilogue warps (448 threads, persistent kernel with
+// 32- to 128-token tiles): warps 8-11 store the results out of a second accumulator while the MMA warp is
+// already filling the other one; TMA and MMA move to warps 12 and 13.
+__host__ __device__ constexpr bool gemm_epi_warps(int nt, bool persist) { return persist && nt >= 32 && nt <= 128; }
+__host__ __device__ constexpr int gemm_threads(int nt, bool persist) { return gemm_epi_warps(nt, persist) ? 448 : 320; }
 constexpr int kAStageCols = kGroup / 2;      // a 128-wide K block of FP16 weights = 64 tensor-memory columns
 // Small activation tiles: three stages and little shared memory, so that two CTAs share an SM and
 // hide each other's latencies. Large tiles: one CTA per SM with as many stages as fit.
@@ -208,14 +214,19 @@ struct GemmParams {
 // PERSIST = false: the CTA's range is known to be one segment (the equal-parts split), and the
 // segment loops below compile to straight-line code.
 template <int NT, bool PERSIST>
-__global__ void __launch_bounds__(kGemmThreads, NT <= 16 ? 2 : 1)
+__global__ void __launch_bounds__(gemm_threads(NT, PERSIST), NT <= 16 ? 2 : 1)
 tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                    const GemmParams prm) {
+    constexpr bool kEpi = gemm_epi_warps(NT, PERSIST);
+    constexpr int kTmaWarp = kEpi ? 12 : 8, kMmaWarp = kEpi ? 13 : 9;
+    constexpr int kAccBufs = kEpi ? 2 : 1;
     constexpr int kStagesG = gemm_stages(NT);
     constexpr int kPackBufs = gemm_pack_bufs(NT);
     constexpr int kBTileBytes = NT * kGroup * 2;
     constexpr int kTmemCols = gemm_tmem_cols(NT);    // accumulator (NT columns) + A stages
     constexpr int kAccCols = NT < 32 ? 32 : NT;
+    constexpr int kAStageBase = kAccBufs * kAccCols;     // tensor-memory columns: accumulator(s), then the A stages
+    static_assert(kAStageBase + kStagesG * kAStageCols <= kTmemCols, "tensor memory budget");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // swizzled operand tiles must start on a 1024-byte boundary of the shared window
     unsigned char *smem = smem_raw + ((1024u - ((uint32_t)__cvta_generic_to_shared(smem_raw) & 1023u)) & 1023u);
@@ -225,8 +236,8 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     uint64_t *bars = reinterpret_cast<uint64_t *>(lut + kLutBytesG);
     // barrier indices
     constexpr int FULL_A = 0, FULL_B = FULL_A + kStagesG, EMPTY = FULL_B + kStagesG, PACK_FULL = EMPTY + kStagesG,
-                  PACK_EMPTY = PACK_FULL + kPackBufs, ACCUM = PACK_EMPTY + kPackBufs, ACC_FREE = ACCUM + 1,
-                  LUT_BAR = ACC_FREE + 1, NUM_BARS = LUT_BAR + 1;
+                  PACK_EMPTY = PACK_FULL + kPackBufs, ACCUM = PACK_EMPTY + kPackBufs, ACC_FREE = ACCUM + 2,
+                  LUT_BAR = ACC_FREE + 2, NUM_BARS = LUT_BAR + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NUM_BARS);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -247,8 +258,10 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             mbar_init(bar(PACK_FULL + p), 1);
             mbar_init(bar(PACK_EMPTY + p), 256);
         }
-        mbar_init(bar(ACCUM), 1);
-        mbar_init(bar(ACC_FREE), 128);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(ACCUM + b), 1);
+            mbar_init(bar(ACC_FREE + b), 128);
+        }
         mbar_init(bar(LUT_BAR), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -266,6 +279,37 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
 
     bool ok = true;
+    // Result of one segment out of accumulator `acc_col` (TMEM lane = weight row r of the tile, read by a
+    // warp whose index modulo 4 names its 32 lanes). A segment that covers the tile's whole K range is
+    // stored as the result; a partial one goes to this CTA's first- or last-segment slot as FP32 and is
+    // added up by the fix-up kernel.
+    auto store_segment = [&](int seg, int len, int n0, int m0, uint32_t acc_col) {
+        const int r = (warp & 3) * 32 + lane;
+        const bool whole = len == groups;
+        float *slot = prm.partials + ((size_t)2 * blockIdx.x + (seg == 0 ? 0 : 1)) * (size_t)(NT * kTileW);
+        const int n = n0 + r;
+#pragma unroll 1
+        for (int c0 = 0; c0 < NT; c0 += 32) {
+            uint32_t v[32];
+            if (NT >= 32 || c0 == 0) {
+                tmem_load32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + acc_col + (uint32_t)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            }
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const int m = m0 + c0 + c;
+                if (c0 + c < NT && m < prm.M && n < prm.N) {
+                    const float f = __uint_as_float(v[c]);
+                    if (!whole)
+                        slot[(c0 + c) * kTileW + r] = f;
+                    else if (prm.y_f32)
+                        static_cast<float *>(prm.y)[(size_t)m * prm.N + n] = f;
+                    else
+                        static_cast<__half *>(prm.y)[(size_t)m * prm.N + n] = __float2half_rn(f);
+                }
+            }
+        }
+    };
     if (warp == kTmaWarp) {
         // ------------------------------------------------------------------ TMA producers
         // lane 1 keeps the queue of packed-byte chunks full, lane 0 feeds the activation tiles;
@@ -314,28 +358,46 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             do {
                 const int tile = it / groups, kb0 = it - tile * groups;
                 const int len = min(groups - kb0, it_end - it);
-                // the previous segment's accumulator must have been read out
-                if (PERSIST && seg > 0) ok = mbar_wait(bar(ACC_FREE), (uint32_t)(seg - 1) & 1u, prm.status);
+                // the accumulator's previous contents must have been read out
+                const int buf = seg % kAccBufs, use = seg / kAccBufs;
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kAccCols);
+                if (PERSIST && use > 0) ok = mbar_wait(bar(ACC_FREE + buf), (uint32_t)(use - 1) & 1u, prm.status);
                 for (int ii = 0; ii < len && ok; ++ii, ++i) {
                     const int s = i % kStagesG;
                     const uint32_t ph = (uint32_t)(i / kStagesG) & 1u;
                     ok = mbar_wait(bar(FULL_A + s), ph, prm.status) && mbar_wait(bar(FULL_B + s), ph, prm.status);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_tmem = tmem_base + (uint32_t)(kAccCols + s * kAStageCols);
+                    const uint32_t a_tmem = tmem_base + (uint32_t)(kAStageBase + s * kAStageCols);
                     const uint32_t b_addr = (uint32_t)__cvta_generic_to_shared(b_tiles + s * kBTileBytes);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {           // eight K = 16 steps; B: two 64-wide swizzle atoms
                         const uint64_t db = umma_desc(b_addr + (j >> 2) * (NT * 128) + (j & 3) * 32);
-                        umma_f16_ts(tmem_base, a_tmem + 8u * j, db, idesc, (ii > 0 || j > 0) ? 1u : 0u);
+                        umma_f16_ts(d_tmem, a_tmem + 8u * j, db, idesc, (ii > 0 || j > 0) ? 1u : 0u);
                     }
                     umma_commit(bar(EMPTY + s));            // the stage is free once these MMAs have read it
                 }
-                if (ok) umma_commit(bar(ACCUM));            // the segment's accumulator is complete
+                if (ok) umma_commit(bar(ACCUM + buf));      // the segment's accumulator is complete
                 it += len;
                 ++seg;
             } while (PERSIST && it < it_end && ok);
         }
+    } else if (kEpi && warp >= 8) {
+        // ------------------------------------------------------------------ epilogue warps 8-11
+        int seg = 0, it = it_begin;
+        do {
+            const int tile = it / groups, kb0 = it - tile * groups;
+            const int len = min(groups - kb0, it_end - it);
+            const int buf = seg % kAccBufs, use = seg / kAccBufs;
+            ok = mbar_wait(bar(ACCUM + buf), (uint32_t)use & 1u, prm.status);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            store_segment(seg, len, (tile / prm.tiles_m) * kTileW, (tile % prm.tiles_m) * NT, (uint32_t)(buf * kAccCols));
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(bar(ACC_FREE + buf));
+            it += len;
+            ++seg;
+        } while (it < it_end);
     } else {
         // ------------------------------------------------------------------ decode (thread = weight row)
         // two groups of four warps take alternate K blocks, so two stages are being filled at a time
@@ -383,7 +445,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             }
             // 64 registers = the row's 128 FP16 weights in decode order, written to this lane of tensor memory
             const uint32_t a_taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) +
-                                     (uint32_t)(kAccCols + s * kAStageCols);
+                                     (uint32_t)(kAStageBase + s * kAStageCols);
             {
                 uint32_t v[32];
 #pragma unroll
@@ -420,39 +482,15 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             if (last_of_chunk) mbar_arrive(bar(PACK_EMPTY + pack_i % kPackBufs));
         }
 
-        // ---------------------------------------------------------------- epilogue (TMEM lane = weight row)
-        // A segment that covers the tile's whole K range is stored as the result; a partial one goes to
-        // this CTA's first- or last-segment slot as FP32 and is added up by the fix-up kernel.
-        if (ok && group == 0) ok = mbar_wait(bar(ACCUM), (uint32_t)seg & 1u, prm.status);
-        if (ok && group == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const bool whole = len == groups;
-            float *slot = prm.partials + ((size_t)2 * blockIdx.x + (seg == 0 ? 0 : 1)) * (size_t)(NT * kTileW);
-            const int n = n0 + r;
-#pragma unroll 1
-            for (int c0 = 0; c0 < NT; c0 += 32) {
-                uint32_t v[32];
-                if (NT >= 32 || c0 == 0) {
-                    tmem_load32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                }
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const int m = m0 + c0 + c;
-                    if (c0 + c < NT && m < prm.M && n < prm.N) {
-                        const float f = __uint_as_float(v[c]);
-                        if (!whole)
-                            slot[(c0 + c) * kTileW + r] = f;
-                        else if (prm.y_f32)
-                            static_cast<float *>(prm.y)[(size_t)m * prm.N + n] = f;
-                        else
-                            static_cast<__half *>(prm.y)[(size_t)m * prm.N + n] = __float2half_rn(f);
-                    }
-                }
+        if (!kEpi) {         // the first decode group also stores the segment's result
+            if (ok && group == 0) ok = mbar_wait(bar(ACCUM), (uint32_t)seg & 1u, prm.status);
+            if (ok && group == 0) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                store_segment(seg, len, n0, m0, 0u);
+                // the accumulator columns may be overwritten by the next segment
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(bar(ACC_FREE));
             }
-            // the accumulator columns may be overwritten by the next segment
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(bar(ACC_FREE));
         }
         it += len;
         ++seg;
@@ -546,7 +584,10 @@ EncodeTiledFn gemm_encode_fn() {
     return fn;
 }
 
-int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M < 1024 ? 128 : 256; }
+int token_tile(int M) {
+    static const int big = getenv("TQ1_GEMM_BIG_TILE") ? atoi(getenv("TQ1_GEMM_BIG_TILE")) : 256;
+    return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M < 1024 ? 128 : big;
+}
 
 // CTAs of a launch: every resident slot (two per SM for the 16-token tiles). With at least as many
 // tiles as slots the iterations are dealt out stream-K fashion; with fewer, every tile is cut into
@@ -599,7 +640,7 @@ int launch_nt(const CUtensorMap &wmap, const CUtensorMap &xmap, const GemmParams
         if (e != cudaSuccess) return cuda_fail(e, "tq1_linear_f16: shared memory opt-in (GEMM)");
         attr_set = true;
     }
-    kern<<<grid, kGemmThreads, smem, stream>>>(wmap, xmap, prm);
+    kern<<<grid, gemm_threads(NT, PERSIST), smem, stream>>>(wmap, xmap, prm);
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: GEMM launch");
     return TQ1_OK;
