@@ -315,6 +315,10 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
             bulk_load(kLutWindowAddr, &g_lut_image, kLutBytes, lut_bar);
         }
     }
+    // A shard of a row-sharded projection will wait for other ranks' flags below: request its weight
+    // tiles first, so that they travel while it waits (weights depend on nothing).
+    if (shard.world > 1 && lane == 0)
+        while (issued < kStages - 1 && issued < n_units) issue_next();
     // Let the next kernel in the stream start its own prologue as SMs free up, then wait until
     // everything before this kernel has finished before touching activations or the workspace.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
