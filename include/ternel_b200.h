@@ -113,6 +113,22 @@ size_t tq1_linear_workspace_bytes(int M, int N, int K);
 int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
                    int M, int N, int K, void *workspace, size_t workspace_bytes, void *stream);
 
+/* Which kernel and which tiling tq1_linear_f16 picks for a shape (host-side, launches nothing).
+ * Stands in for the reference's recorded dispatch rules select_lut23 / select_gemm
+ * (src/ternel_mlx/modules.py:331-422), which its tests replay against committed sweeps
+ * (tests/test_mlx_modules.py:553-1084); here the sweep is ternel_b200/dispatch_sweep_b200.json.
+ *   aligned     1 if blocks and x are 16-byte aligned (the fast kernels need it)
+ *   kernel      TQ1_KERNEL_*;  token_tile / ctas / parts: tensor-core kernel only (activation rows
+ *               per tile, CTAs launched, equal K parts per tile or 0 for the stream-K split) */
+#define TQ1_KERNEL_ROWS 0
+#define TQ1_KERNEL_STREAM_GEMV 1
+#define TQ1_KERNEL_TENSOR_CORE 2
+int tq1_linear_plan(int M, int N, int K, int aligned, int *kernel, int *token_tile, int *ctas, int *parts);
+
+/* For recording sweeps only: force the tensor-core kernel's token tile (16..256) for every
+ * later call of this process; 0 restores the rule. Not thread-safe. No reference counterpart. */
+int tq1_debug_force_token_tile(int token_tile);
+
 /* ---- row-sharded linear over several GPUs -------------------------------- */
 
 /* One rank's view of an output-row shard. Output rows are independent, so rank r owns rows

@@ -38,6 +38,27 @@ int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
     return launch_gemv_rows(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, s);
 }
 
+int tq1_linear_plan(int M, int N, int K, int aligned, int *kernel, int *token_tile, int *ctas, int *parts) {
+    if (!kernel || !token_tile || !ctas || !parts) return fail(TQ1_ERR_INVALID, "tq1_linear_plan: null pointer");
+    if (M <= 0 || N <= 0 || K <= 0 || K % kGroup) return fail(TQ1_ERR_INVALID, "tq1_linear_plan: bad shape");
+    *token_tile = *ctas = *parts = 0;
+    if (M == 1 && aligned && gemv_stream_shape_ok(N, K)) {
+        *kernel = TQ1_KERNEL_STREAM_GEMV;
+    } else if (aligned && gemm_tc_shape_ok(M, N, K)) {
+        *kernel = TQ1_KERNEL_TENSOR_CORE;
+        gemm_tc_plan(M, N, K, token_tile, ctas, parts);
+    } else {
+        *kernel = TQ1_KERNEL_ROWS;
+    }
+    return TQ1_OK;
+}
+
+int tq1_debug_force_token_tile(int token_tile) {
+    if (gemm_tc_force_tile(token_tile) != TQ1_OK)
+        return fail(TQ1_ERR_INVALID, "tq1_debug_force_token_tile: %d is not 0, 16, 32, 64, 128 or 256", token_tile);
+    return TQ1_OK;
+}
+
 static size_t shard_local_bytes(int M, int N_local) {
     return ((size_t)M * N_local * sizeof(__half) + 255) & ~(size_t)255;
 }

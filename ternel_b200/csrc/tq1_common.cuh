@@ -72,6 +72,8 @@ bool gemm_tc_supported(const uint8_t *blocks, const __half *x, int M, int N, int
 size_t gemm_tc_workspace_bytes(int M, int N, int K);
 int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int M, int N, int K,
                    void *workspace, cudaStream_t stream);
+void gemm_tc_plan(int M, int N, int K, int *tile, int *ctas, int *parts);
+int gemm_tc_force_tile(int nt);
 
 // Five base-3 digits of a byte packed two bits each (digit i at bits 2i..2i+1).
 __host__ __device__ inline uint32_t trits_2bit(uint32_t byte) {

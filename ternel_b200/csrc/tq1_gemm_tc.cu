@@ -584,17 +584,7 @@ EncodeTiledFn gemm_encode_fn() {
     return fn;
 }
 
-int token_tile(int M) {
-    static const int big = getenv("TQ1_GEMM_BIG_TILE") ? atoi(getenv("TQ1_GEMM_BIG_TILE")) : 256;
-    return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M < 1024 ? 128 : big;
-}
-
-// CTAs of a launch: every resident slot (two per SM for the 16-token tiles). With at least as many
-// tiles as slots the iterations are dealt out stream-K fashion; with fewer, every tile is cut into
-// equal parts of at least eight K blocks.
-WorkSplit pick_work(int M, int N, int K) {
-    const int nt = token_tile(M);
-    const long long tiles = (long long)((N + kTileW - 1) / kTileW) * ((M + nt - 1) / nt);
+int sm_count_cached() {
     static int sm_count = 0;
     if (!sm_count) {
         int dev = 0;
@@ -602,7 +592,13 @@ WorkSplit pick_work(int M, int N, int K) {
         if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
             sm_count = 148;
     }
-    const long long slots = (long long)sm_count * (nt <= 16 ? 2 : 1);
+    return sm_count;
+}
+
+// How the (tile, K block) iterations of a shape are dealt out for a given token tile.
+WorkSplit split_work(int nt, int M, int N, int K) {
+    const long long tiles = (long long)((N + kTileW - 1) / kTileW) * ((M + nt - 1) / nt);
+    const long long slots = (long long)sm_count_cached() * (nt <= 16 ? 2 : 1);
     WorkSplit w;
     w.groups = K / kGroup;
     w.total_iters = (int)(tiles * w.groups);
@@ -621,6 +617,38 @@ WorkSplit pick_work(int M, int N, int K) {
     w.rem = w.total_iters % w.ctas;
     return w;
 }
+
+// Activation rows per tile. Up to 16 rows always take the 16-row tile. Beyond that the tile with
+// the smallest modelled time wins: (K blocks a CTA processes) x (time per K block of that tile) +
+// (segments a CTA stores) x (time to store one), with the five pairs of constants fitted to the
+// recorded sweep in ternel_b200/dispatch_sweep_b200.json (tests replay the file: the choice is within
+// 10% of the best recorded tile for every case). g_forced_tile overrides the rule while a sweep is
+// being recorded.
+int g_forced_tile = 0;
+int token_tile(int M, int N, int K) {
+    if (g_forced_tile) return g_forced_tile;
+    if (M <= 16) return 16;
+    static const int tiles[5] = {16, 32, 64, 128, 256};
+    static const float per_block_us[5] = {0.8f, 0.55f, 0.55f, 0.7f, 1.1f};
+    static const float per_store_us[5] = {0.0f, 1.0f, 2.0f, 2.0f, 12.0f};
+    int best = 128;
+    float best_cost = 0.0f;
+    for (int i = 0; i < 5; ++i) {
+        const int nt = tiles[i];
+        if (nt > 16 && nt >= 4 * M) continue;           // a tile mostly of padding
+        const WorkSplit w = split_work(nt, M, N, K);
+        const float blocks = w.splits ? (float)((w.groups + w.splits - 1) / w.splits) : (float)w.total_iters / w.ctas;
+        const float stores = w.splits ? 1.0f : blocks / w.groups + 1.0f;
+        const float cost = blocks * per_block_us[i] + stores * per_store_us[i];
+        if (i == 0 || cost < best_cost) { best = nt; best_cost = cost; }
+    }
+    return best;
+}
+
+// CTAs of a launch: every resident slot (two per SM for the 16-token tiles). With at least as many
+// tiles as slots the iterations are dealt out stream-K fashion; with fewer, every tile is cut into
+// equal parts of at least eight K blocks.
+WorkSplit pick_work(int M, int N, int K) { return split_work(token_tile(M, N, K), M, N, K); }
 
 size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -648,6 +676,19 @@ int launch_nt(const CUtensorMap &wmap, const CUtensorMap &xmap, const GemmParams
 
 }  // namespace
 
+int gemm_tc_force_tile(int nt) {
+    if (nt != 0 && nt != 16 && nt != 32 && nt != 64 && nt != 128 && nt != 256) return TQ1_ERR_INVALID;
+    g_forced_tile = nt;
+    return TQ1_OK;
+}
+
+void gemm_tc_plan(int M, int N, int K, int *tile, int *ctas, int *parts) {
+    const WorkSplit w = pick_work(M, N, K);
+    *tile = token_tile(M, N, K);
+    *ctas = w.ctas;
+    *parts = w.splits;
+}
+
 bool gemm_tc_shape_ok(int M, int N, int K) {
     return M >= 2 && N >= 1 && K % (kPackGroups * kGroup) == 0;
 }
@@ -658,7 +699,7 @@ bool gemm_tc_supported(const uint8_t *blocks, const __half *x, int M, int N, int
 }
 
 size_t gemm_tc_workspace_bytes(int M, int N, int K) {
-    const size_t slots = (size_t)2 * pick_work(M, N, K).ctas * token_tile(M) * kTileW * sizeof(float);
+    const size_t slots = (size_t)2 * pick_work(M, N, K).ctas * token_tile(M, N, K) * kTileW * sizeof(float);
     return kWsScratchOffset + align256((size_t)M * K * sizeof(__half)) + align256(slots);
 }
 
@@ -670,7 +711,7 @@ int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, 
     unsigned *status = reinterpret_cast<unsigned *>(ws);
     __half *xperm = reinterpret_cast<__half *>(ws + kWsScratchOffset);
     float *partials = reinterpret_cast<float *>(ws + kWsScratchOffset + align256((size_t)M * K * sizeof(__half)));
-    const int nt = token_tile(M);
+    const int nt = token_tile(M, N, K);
     const WorkSplit work = pick_work(M, N, K);
     const int ctas = work.ctas;
 

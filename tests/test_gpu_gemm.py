@@ -138,3 +138,20 @@ def test_prefill_shapes_full_size(rows, columns, batch):
     assert o.normalised_error(got32[:8], want32) < F32_TOL
     doubled = run_linear(blocks, (x[:128].astype(np.float32) * 2).astype(np.float16))
     np.testing.assert_array_equal(doubled, got32 * 2)
+
+
+@pytest.mark.parametrize(("rows", "columns", "batch"), ((1000, 1536, 17), (5120, 5120, 100), (640, 5120, 300)))
+def test_every_token_tile_gives_the_right_answer(rows, columns, batch):
+    """The dispatch rule may pick any token tile for a batch size: all five must be correct for it."""
+    from ternel_b200 import _native
+    lib = _native.lib()
+    blocks, rng = random_blocks(rows, columns, seed=rows + batch)
+    x = rng.standard_normal((batch, columns)).astype(np.float16)
+    want = o.float64_matmul(blocks, x, rows=rows, columns=columns)
+    try:
+        for tile in (16, 32, 64, 128, 256):
+            assert lib.tq1_debug_force_token_tile(tile) == 0
+            assert o.normalised_error(run_linear(blocks, x), want) < F32_TOL, tile
+        assert lib.tq1_debug_force_token_tile(48) == _native.TQ1_ERR_INVALID
+    finally:
+        assert lib.tq1_debug_force_token_tile(0) == 0
