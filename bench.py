@@ -321,7 +321,7 @@ def run_gpu_arm(args) -> None:
                 "algorithmic_bytes_per_launch_avg": alg_bytes_rank / stack.launches_per_step,
                 "avg_launch_us": ms_per_step * 1e3 / stack.launches_per_step,
                 # DRAM bytes per launch: the ncu capture of one launch of each of the four shapes
-                # (profiles/gemv_stream_decode_step_batch1.md) read 72.93 MB against 72.42 MB of
+                # (the committed ncu summary of the batch-1 kernel) read 72.93 MB against 72.42 MB of
                 # algorithmic bytes; traffic grows with the units processed, so the ratio carries over.
                 # Only the fused batch-1 single-GPU step was captured.
                 "traffic": (NCU_TRAFFIC_RATIO * alg_bytes_rank / stack.launches_per_step

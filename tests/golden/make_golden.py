@@ -88,7 +88,13 @@ def _write_sidecars(fmt, reorder) -> None:
         handle.seek(0)
         handle.write(header.pack())
     fmt.read_sidecar(path)                                   # the reference's own reader accepts it
-    reorder.reorder_sidecar(path, HERE / "sidecar_small.lut23")
+    import os
+    cwd = os.getcwd()
+    os.chdir(HERE)              # the LUT23 manifest records the source path as given: keep it relative
+    try:
+        reorder.reorder_sidecar(Path(path.name), Path("sidecar_small.lut23"))
+    finally:
+        os.chdir(cwd)
     np.savez_compressed(HERE / "sidecar_small_blocks.npz", **{name: blocks for name, _, _, blocks in tensors})
     print("wrote sidecar_small.tq1g128, sidecar_small.lut23, sidecar_small_blocks.npz")
 
