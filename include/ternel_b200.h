@@ -113,6 +113,15 @@ size_t tq1_linear_workspace_bytes(int M, int N, int K);
 int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
                    int M, int N, int K, void *workspace, size_t workspace_bytes, void *stream);
 
+/* Gated feed-forward input in one call: blocks holds 2N rows, gate row i at row 2i and up row i at
+ * row 2i + 1 (interleave the two packed matrices once at load: rows are independent byte ranges),
+ * and y[m][i] = silu(gate_i . x_m) * (up_i . x_m) with the dot products and the activation in FP32
+ * and one narrowing at the store. Replaces two tq1_matmul calls plus the elementwise nn.silu(gate) * up
+ * of the converted model's MLP (the reference computes those as separate graph nodes). Needs
+ * K % 512 == 0 and 16-byte aligned blocks and x; workspace as for tq1_linear_f16(M, 2N, K). */
+int tq1_linear_swiglu_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32, int M, int N, int K,
+                          void *workspace, size_t workspace_bytes, void *stream);
+
 /* Which kernel and which tiling tq1_linear_f16 picks for a shape (host-side, launches nothing).
  * Stands in for the reference's recorded dispatch rules select_lut23 / select_gemm
  * (src/ternel_mlx/modules.py:331-422), which its tests replay against committed sweeps

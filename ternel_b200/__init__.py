@@ -24,7 +24,8 @@ def __getattr__(name):
     if name in ("replace_with_packed", "expect_counts", "blocks_from_ternary"):
         from . import packed_model
         return getattr(packed_model, name)
-    if name in ("tq1_matmul", "tq1_gemm", "tq1_get_rows", "validate_device_blocks"):
+    if name in ("tq1_matmul", "tq1_gemm", "tq1_get_rows", "validate_device_blocks", "tq1_swiglu",
+                "interleave_gate_up"):
         from . import ops
         return getattr(ops, name)
     raise AttributeError(name)

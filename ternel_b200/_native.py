@@ -32,6 +32,8 @@ SIGNATURES = {
     "tq1_linear_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tq1_linear_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                c_void_p, c_size_t, c_void_p]),
+    "tq1_linear_swiglu_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                      c_void_p, c_size_t, c_void_p]),
     "tq1_linear_plan": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int),
                                 POINTER(c_int)]),
     "tq1_debug_force_token_tile": (c_int, [c_int]),

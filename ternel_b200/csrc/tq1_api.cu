@@ -38,6 +38,32 @@ int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
     return launch_gemv_rows(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, s);
 }
 
+int tq1_linear_swiglu_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32, int M, int N, int K,
+                          void *workspace, size_t workspace_bytes, void *stream) {
+    if (!blocks || !x || !y) return fail(TQ1_ERR_INVALID, "tq1_linear_swiglu_f16: null pointer");
+    if (M <= 0) return fail(TQ1_ERR_INVALID, "activations have an empty batch dimension");
+    if (N <= 0 || K <= 0) return fail(TQ1_ERR_INVALID, "tensor dimensions must be positive, got %dx%d", N, K);
+    if (N > (1 << 30)) return fail(TQ1_ERR_INVALID, "tq1_linear_swiglu_f16: too many rows");
+    const int rows = 2 * N;                 // (gate, up) pairs
+    if (reinterpret_cast<uintptr_t>(x) & 15)
+        return fail(TQ1_ERR_INVALID, "tq1_linear_swiglu_f16: x must be 16-byte aligned");
+    const __half *xh = static_cast<const __half *>(x);
+    const bool gemv = M == 1 && gemv_stream_supported(blocks, rows, K);
+    if (!gemv && !gemm_tc_supported(blocks, xh, M, rows, K))
+        return fail(TQ1_ERR_INVALID,
+                    "tq1_linear_swiglu_f16: needs K %% 512 == 0 and 16-byte aligned blocks (got %dx%d)", rows, K);
+    const size_t need = tq1_linear_workspace_bytes(M, rows, K);
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
+        return fail(TQ1_ERR_WORKSPACE, "tq1_linear_swiglu_f16: workspace of %zu bytes (256-byte aligned) required", need);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (gemv) {
+        ShardDev opt = {};
+        opt.swiglu = 1;
+        return launch_gemv_stream(blocks, xh, y, y_is_f32 != 0, rows, K, workspace, s, &opt);
+    }
+    return launch_gemm_tc(blocks, xh, y, y_is_f32 != 0, M, rows, K, workspace, s, true);
+}
+
 int tq1_linear_plan(int M, int N, int K, int aligned, int *kernel, int *token_tile, int *ctas, int *parts) {
     if (!kernel || !token_tile || !ctas || !parts) return fail(TQ1_ERR_INVALID, "tq1_linear_plan: null pointer");
     if (M <= 0 || N <= 0 || K <= 0 || K % kGroup) return fail(TQ1_ERR_INVALID, "tq1_linear_plan: bad shape");

@@ -52,6 +52,7 @@ struct ShardDev {
     int wait_tiles;                     // how many of them exist
     unsigned wait_epoch;
     int ld_total;                       // row length of the gathered output (elements)
+    int swiglu;                         // unsharded only: rows are (gate, up) pairs, y[i] = silu(gate_i) * up_i
 };
 
 // Streaming batch-1 GEMV (TMA + integer tensor cores); needs K % 512 == 0 and 16-byte aligned blocks.
@@ -71,7 +72,10 @@ bool gemm_tc_shape_ok(int M, int N, int K);
 bool gemm_tc_supported(const uint8_t *blocks, const __half *x, int M, int N, int K);
 size_t gemm_tc_workspace_bytes(int M, int N, int K);
 int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int M, int N, int K,
-                   void *workspace, cudaStream_t stream);
+                   void *workspace, cudaStream_t stream, bool swiglu = false);
+
+// silu(gate) * up in FP32, the activation of a gated feed-forward block
+__host__ __device__ inline float swiglu_f32(float gate, float up) { return gate / (1.0f + expf(-gate)) * up; }
 void gemm_tc_plan(int M, int N, int K, int *tile, int *ctas, int *parts);
 int gemm_tc_force_tile(int nt);
 

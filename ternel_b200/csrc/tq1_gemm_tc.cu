@@ -209,6 +209,7 @@ struct GemmParams {
     int tiles_m;              // activation tiles; output tile t covers weight tile t / tiles_m, token tile t % tiles_m
     WorkSplit work;           // which (tile, K block) iterations each CTA takes
     int y_f32;
+    int swiglu;               // weight rows are (gate, up) pairs: y[m][n / 2] = silu(gate) * up, row length N / 2
 };
 
 // PERSIST = false: the CTA's range is known to be one segment (the equal-parts split), and the
@@ -298,6 +299,17 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
                 const int m = m0 + c0 + c;
+                if (whole && prm.swiglu) {          // the even row of a (gate, up) pair stores the product
+                    const float gate = __uint_as_float(v[c]);
+                    const float up = __shfl_down_sync(0xffffffffu, gate, 1);
+                    if (c0 + c < NT && m < prm.M && n + 1 < prm.N && (r & 1) == 0) {
+                        const float out = swiglu_f32(gate, up);
+                        const size_t o = (size_t)m * (prm.N >> 1) + (n >> 1);
+                        if (prm.y_f32) static_cast<float *>(prm.y)[o] = out;
+                        else static_cast<__half *>(prm.y)[o] = __float2half_rn(out);
+                    }
+                    continue;
+                }
                 if (c0 + c < NT && m < prm.M && n < prm.N) {
                     const float f = __uint_as_float(v[c]);
                     if (!whole)
@@ -520,7 +532,7 @@ __global__ void tq1_permute_x_kernel(const __half *__restrict__ x, __half *__res
 constexpr int kFixCols = 4;
 __global__ void __launch_bounds__(kTileW)
 tq1_streamk_fixup_kernel(const float *__restrict__ partials, void *__restrict__ y, int y_f32,
-                         int M, int N, int tiles_m, const WorkSplit work, int nt) {
+                         int M, int N, int tiles_m, const WorkSplit work, int nt, int swiglu) {
     const int groups = work.groups, ctas = work.ctas;
     int c_lo, c_hi, tile, it0;
     if (work.splits > 0) {                       // every tile in equal parts: blockIdx.x names the tile
@@ -542,7 +554,7 @@ tq1_streamk_fixup_kernel(const float *__restrict__ partials, void *__restrict__ 
     const int n = (tile / tiles_m) * kTileW + r;
     const int m0 = (tile % tiles_m) * nt;
     const int c0 = blockIdx.y * kFixCols;
-    if (n >= N) return;
+    const bool live = n < N;
     float total[kFixCols];
 #pragma unroll
     for (int c = 0; c < kFixCols; ++c) total[c] = 0.0f;
@@ -552,13 +564,23 @@ tq1_streamk_fixup_kernel(const float *__restrict__ partials, void *__restrict__ 
         const float *slot = partials + ((size_t)2 * cta + which) * (size_t)(nt * kTileW) + (size_t)c0 * kTileW + r;
         float v[kFixCols];
 #pragma unroll
-        for (int c = 0; c < kFixCols; ++c) v[c] = m0 + c0 + c < M ? slot[c * kTileW] : 0.0f;
+        for (int c = 0; c < kFixCols; ++c) v[c] = live && m0 + c0 + c < M ? slot[c * kTileW] : 0.0f;
 #pragma unroll
         for (int c = 0; c < kFixCols; ++c) total[c] += v[c];
     }
 #pragma unroll
     for (int c = 0; c < kFixCols; ++c) {
-        if (m0 + c0 + c < M) {
+        if (swiglu) {                       // (gate, up) row pairs: the even row stores silu(gate) * up
+            const float up = __shfl_down_sync(0xffffffffu, total[c], 1);
+            if (live && n + 1 < N && (r & 1) == 0 && m0 + c0 + c < M) {
+                const float out = swiglu_f32(total[c], up);
+                const size_t o = (size_t)(m0 + c0 + c) * (N >> 1) + (n >> 1);
+                if (y_f32) static_cast<float *>(y)[o] = out;
+                else static_cast<__half *>(y)[o] = __float2half_rn(out);
+            }
+            continue;
+        }
+        if (live && m0 + c0 + c < M) {
             const size_t o = (size_t)(m0 + c0 + c) * N + n;
             if (y_f32) static_cast<float *>(y)[o] = total[c];
             else static_cast<__half *>(y)[o] = __float2half_rn(total[c]);
@@ -704,7 +726,7 @@ size_t gemm_tc_workspace_bytes(int M, int N, int K) {
 }
 
 int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int M, int N, int K,
-                   void *workspace, cudaStream_t stream) {
+                   void *workspace, cudaStream_t stream, bool swiglu) {
     EncodeTiledFn encode = gemm_encode_fn();
     if (!encode) return fail(TQ1_ERR_CUDA, "tq1_linear_f16: cuTensorMapEncodeTiled is unavailable");
     unsigned char *ws = static_cast<unsigned char *>(workspace);
@@ -754,6 +776,7 @@ int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, 
     prm.tiles_m = (M + nt - 1) / nt;
     prm.work = work;
     prm.y_f32 = y_f32 ? 1 : 0;
+    prm.swiglu = swiglu ? 1 : 0;
     dim3 grid((unsigned)ctas);
     int rc;
     if (work.splits > 0)        // one segment per CTA
@@ -774,7 +797,7 @@ int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, 
         const unsigned fix_blocks = work.splits > 0 ? (unsigned)(ctas / work.splits) : (unsigned)(ctas - 1);
         const unsigned col_blocks = (unsigned)(((M < nt ? M : nt) + kFixCols - 1) / kFixCols);
         tq1_streamk_fixup_kernel<<<dim3(fix_blocks, col_blocks), kTileW, 0, stream>>>(
-            partials, y, prm.y_f32, M, N, prm.tiles_m, work, nt);
+            partials, y, prm.y_f32, M, N, prm.tiles_m, work, nt, prm.swiglu);
         err = cudaGetLastError();
         if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: stream-K fix-up launch");
     }

@@ -610,6 +610,14 @@ tq1_gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half *_
                         asm volatile("st.release.sys.global.u32 [%0], %1;"
                                      ::"l"(shard.peer_flags[lane] + tt), "r"(epoch) : "memory");
                     }
+                } else if (shard.swiglu) {
+                    // rows come as (gate, up) pairs: the even lane of a pair stores silu(gate) * up
+                    const float up = __shfl_down_sync(0xffffffffu, total, 1);
+                    if (hf == 0 && (r & 1) == 0 && row + 1 < N) {
+                        const float out = swiglu_f32(total, up);
+                        if (OUT_F32) static_cast<float *>(y)[row >> 1] = out;
+                        else static_cast<__half *>(y)[row >> 1] = __float2half_rn(out);
+                    }
                 } else if (hf == 0 && row < N) {
                     if (OUT_F32) static_cast<float *>(y)[row] = total;
                     else static_cast<__half *>(y)[row] = __float2half_rn(total);
@@ -675,13 +683,14 @@ static int launch_gemv_rows_block(const uint8_t *blocks, const __half *x, void *
 int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K,
                        void *workspace, cudaStream_t stream, const ShardDev *shard) {
     const int step = rows_per_launch(N, K);
-    if (step < N && shard)
+    if (step < N && shard && shard->world > 1)
         return fail(TQ1_ERR_INVALID, "tq1_linear_f16_sharded: a shard of %d rows is too tall for one launch", N);
+    const int yshift = shard && shard->swiglu ? 1 : 0;        // paired rows give one output per two rows
     const size_t row_bytes = (size_t)(K / kGroup) * kBlockBytes;
     for (int n0 = 0; n0 < N; n0 += step) {
         const int rows = N - n0 < step ? N - n0 : step;
-        void *yb = y_f32 ? static_cast<void *>(static_cast<float *>(y) + n0)
-                         : static_cast<void *>(static_cast<__half *>(y) + n0);
+        void *yb = y_f32 ? static_cast<void *>(static_cast<float *>(y) + (n0 >> yshift))
+                         : static_cast<void *>(static_cast<__half *>(y) + (n0 >> yshift));
         const int rc = launch_gemv_rows_block(blocks + (size_t)n0 * row_bytes, x, y ? yb : nullptr, y_f32, rows, K,
                                               workspace, stream, shard);
         if (rc != TQ1_OK) return rc;

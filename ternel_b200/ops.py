@@ -82,6 +82,27 @@ def _(blocks, x, out_f32):
     return x.new_empty((x.shape[0], blocks.shape[0]), dtype=torch.float32 if out_f32 else torch.float16)
 
 
+@torch.library.custom_op("ternel::tq1_linear_swiglu", mutates_args=(), device_types="cuda")
+def _tq1_linear_swiglu_op(blocks: torch.Tensor, x: torch.Tensor, out_f32: bool) -> torch.Tensor:
+    rows = blocks.shape[0]
+    batch, columns = x.shape
+    out = torch.empty((batch, rows // 2), dtype=torch.float32 if out_f32 else torch.float16, device=x.device)
+    lib = _native.lib()
+    need = lib.tq1_linear_workspace_bytes(batch, rows, columns)
+    ws = _workspace(x.device, need)
+    with torch.cuda.device(x.device):
+        check(lib.tq1_linear_swiglu_f16(blocks.data_ptr(), x.data_ptr(), out.data_ptr(), int(out_f32),
+                                        batch, rows // 2, columns,
+                                        ws.data_ptr() if ws is not None else None,
+                                        ws.numel() if ws is not None else 0, _stream_ptr(x.device)))
+    return out
+
+
+@_tq1_linear_swiglu_op.register_fake
+def _(blocks, x, out_f32):
+    return x.new_empty((x.shape[0], blocks.shape[0] // 2), dtype=torch.float32 if out_f32 else torch.float16)
+
+
 @torch.library.custom_op("ternel::tq1_embedding", mutates_args=(), device_types="cuda")
 def _tq1_embedding_op(blocks: torch.Tensor, ids: torch.Tensor, out_f32: bool) -> torch.Tensor:
     rows, groups = blocks.shape[0], blocks.shape[1]
@@ -163,6 +184,33 @@ def tq1_matmul(blocks: torch.Tensor, x: torch.Tensor, *, out_dtype: torch.dtype 
     if blocks.device != x.device:
         raise FormatError(f"blocks on {blocks.device} but activations on {x.device}")
     return _tq1_linear_op(blocks, x.contiguous(), out_dtype == torch.float32)
+
+
+def tq1_swiglu(blocks: torch.Tensor, x: torch.Tensor, *, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``silu(x @ Wg.T) * (x @ Wu.T)`` in one call, for ``blocks`` holding the gate and up rows interleaved
+    (row ``2i`` = gate row ``i``, row ``2i + 1`` = up row ``i``; see ``interleave_gate_up``). Dot products and
+    the activation are FP32, with one narrowing at the store. Result ``(batch, rows / 2)``."""
+    rows, groups = _check_blocks(blocks)
+    if rows % 2:
+        raise FormatError(f"{rows} rows cannot be (gate, up) pairs")
+    _check_activations(x, groups)
+    out_dtype = out_dtype or x.dtype
+    if out_dtype not in OUTPUT_DTYPES:
+        raise FormatError(f"output dtype must be one of {OUTPUT_DTYPES}, got {out_dtype}")
+    _require_cuda(blocks, "blocks")
+    _require_cuda(x, "activations")
+    if blocks.device != x.device:
+        raise FormatError(f"blocks on {blocks.device} but activations on {x.device}")
+    return _tq1_linear_swiglu_op(blocks, x.contiguous(), out_dtype == torch.float32)
+
+
+def interleave_gate_up(gate_blocks: torch.Tensor, up_blocks: torch.Tensor) -> torch.Tensor:
+    """Canonical blocks with gate row ``i`` at row ``2i`` and up row ``i`` at row ``2i + 1`` (a byte copy)."""
+    _check_blocks(gate_blocks)
+    _check_blocks(up_blocks)
+    if gate_blocks.shape != up_blocks.shape:
+        raise FormatError(f"gate {tuple(gate_blocks.shape)} and up {tuple(up_blocks.shape)} differ in shape")
+    return torch.stack((gate_blocks, up_blocks), dim=1).reshape(2 * gate_blocks.shape[0], *gate_blocks.shape[1:]).contiguous()
 
 
 # The reference exposes the prefill kernel under its own name; here both names
