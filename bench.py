@@ -290,7 +290,7 @@ def run_gpu_arm(args) -> None:
     # end-to-end through the public operator API with host buffers
     e2e = None
     if not args.skip_e2e:
-        e2e = measure_e2e(args, stack, device, world, barrier)
+        e2e = measure_e2e(args, stack, device, world, barrier, one_step)
 
     checksum = stack.checksum()
     status = int(stack.workspace[:4].view(torch.int32)[0].item())
@@ -489,8 +489,9 @@ def measure_step_batch8(args, stack, device, replays: int = 10):
             "gbps": stack8.algorithmic_bytes_per_step / (ms / 1e3) / 1e9, "checksum": stack8.checksum()}
 
 
-def measure_e2e(args, stack, device, world, barrier):
-    """Same step through the torch custom ops, inputs in pinned host memory every step."""
+def measure_e2e(args, stack, device, world, barrier, one_step):
+    """Same step through the public API, inputs in pinned host memory every step: the torch custom ops on
+    one GPU; on several GPUs the sharded entry (LayerStack's captured step with kernel-side pushes)."""
     import torch
     import torch.distributed as dist
     from ternel_b200.ops import tq1_get_rows, tq1_matmul
@@ -524,7 +525,18 @@ def measure_e2e(args, stack, device, world, barrier):
         from ternel_b200.graphs import GraphedStep
         graphed = GraphedStep(forward, [stack.ids] + [stack.inputs[k] for k in keys])
 
+    sharded = world > 1 and stack.exchange == "p2p"
+
     def step():
+        if sharded:                     # host -> the stack's static inputs, its captured step, device -> host
+            stack.ids.copy_(host_ids, non_blocking=True)
+            for k in keys:
+                stack.inputs[k].copy_(host_x[k], non_blocking=True)
+            one_step()
+            for n, buf in last:
+                buf.copy_(stack.outputs[n], non_blocking=True)
+            torch.cuda.synchronize()
+            return
         if graphed is not None:         # host -> static device inputs, one graph replay, device -> host
             outs = graphed(host_ids, *[host_x[k] for k in keys])
         else:
@@ -550,8 +562,10 @@ def measure_e2e(args, stack, device, world, barrier):
     return {"value": stack.algorithmic_bytes_per_step * world / sec / 1e9, "unit": UNIT,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": sec * 1e3,
             "steps": steps,
-            "api": "torch.ops.ternel.tq1_linear / tq1_embedding, one call per projection"
-                   + (", captured once by ternel_b200.graphs.GraphedStep and replayed" if graphed is not None else "")}
+            "api": ("ternel_b200.stack.LayerStack.step (tq1_linear_f16_sharded per projection, tq1_embedding_f16), "
+                    "captured once as a CUDA graph and replayed" if sharded else
+                    "torch.ops.ternel.tq1_linear / tq1_embedding, one call per projection"
+                    + (", captured once by ternel_b200.graphs.GraphedStep and replayed" if graphed is not None else ""))}
 
 
 def main():
