@@ -58,6 +58,9 @@ def parse_args():
                    help="run only the batched side measurement on these cases, e.g. '2:17408x5120,2048:5120x17408' "
                         "(M:NxK), print its JSON and exit; with --ring to choose the number of distinct weight buffers")
     p.add_argument("--ring", type=int, default=14, help="distinct weight buffers per shape in the batched measurement")
+    p.add_argument("--only-gather", type=int, default=0, metavar="TOKENS",
+                   help="time only the packed-embedding gather of this many token ids (151936 x 5120 table), "
+                        "print its JSON and exit")
     return p.parse_args()
 
 
@@ -286,6 +289,7 @@ def run_gpu_arm(args) -> None:
     batched = measure_batched(device) if world == 1 and not args.skip_batched else None
     if batched is not None and args.batch == 1:
         batched["decode_step_batch8"] = measure_step_batch8(args, stack, device)
+        batched["gather"] = [measure_gather(tokens, table=stack.table) for tokens in (512, 8192)]
 
     # end-to-end through the public operator API with host buffers
     e2e = None
@@ -455,6 +459,61 @@ def measure_batched(device, replays: int = 3, cases=None, ring_size: int = 14):
     return out
 
 
+def measure_gather(tokens: int, vocab: int = 151936, hidden: int = 5120, replays: int = 20, table=None):
+    """The packed-embedding gather on its own: `tokens` random ids per call, checked against the oracle on a
+    sample, timed with CUDA events. Algorithmic bytes per token: 28*K/128 read + 2*K written."""
+    import numpy as np
+    import torch
+    from oracle import tq1_oracle as o
+    from ternel_b200.ops import tq1_get_rows
+    from ternel_b200.stack import random_blocks_device
+
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(5)
+    if table is None:
+        table = random_blocks_device(vocab, hidden, gen, device)
+    vocab, hidden = table.shape[0], table.shape[1] * 128
+    ids = torch.randint(0, vocab, (tokens,), generator=gen, device=device)
+    out = tq1_get_rows(table, ids)
+    torch.cuda.synchronize()
+    sample = ids[:8].cpu().numpy()
+    sample_rows = table[ids[:8]].cpu().numpy()            # only the sampled rows leave the device
+    want = o.get_rows(sample_rows, np.arange(sample.size), rows=sample.size, columns=hidden, dtype=np.float16)
+    assert np.array_equal(out[:8].cpu().numpy(), want), "gather parity failed before timing"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)        # larger than L2
+    pairs = 8
+
+    def timed_graph(with_gather: bool) -> float:
+        """Device time of `pairs` x (L2 flush [+ gather]) captured as one CUDA graph, per pair, in us."""
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            flush.zero_()
+            torch.cuda.synchronize()
+        with torch.cuda.graph(graph):
+            for _ in range(pairs):
+                flush.zero_()
+                if with_gather:
+                    tq1_get_rows(table, ids)
+        graph.replay()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(replays):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) * 1e3 / (replays * pairs)
+
+    us = timed_graph(True) - timed_graph(False)      # the flush alone is timed the same way and subtracted
+    alg = tokens * (hidden // 128 * 28 + 2 * hidden)
+    return {"tokens": tokens, "us": us, "gbps": alg / us / 1e3, "algorithmic_bytes": alg,
+            "l2_policy": "256 MiB written between calls (its time measured alone and subtracted), CUDA-graph replays"}
+
+
 def measure_step_batch8(args, stack, device, replays: int = 10):
     """The same 64-layer step with eight sequences per step (the small-batch kernel), over the same
     resident weights; graph-timed like the headline step."""
@@ -572,6 +631,8 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.only_gather:
+        print(json.dumps({"gather": measure_gather(args.only_gather)}))
     elif args.only_batched:
         import torch
         cases = []
