@@ -36,26 +36,26 @@ static void scan_host(const uint8_t *blocks, int64_t groups, int64_t *bad_full, 
     *bad_tail = bt;
 }
 
-// One thread per block; per-CTA counts are combined with one atomic each.
-__global__ void __launch_bounds__(256) validate_kernel(const uint32_t *__restrict__ words,
+// The blocks are scanned as a flat array of 32-bit words, consecutive threads on consecutive words
+// (coalesced). Word i of the array is word i % 7 of its block: word 0 holds the scale and two code
+// bytes, words 1..5 four code bytes, word 6 three code bytes and the tail byte. Bytes above the limit
+// are counted four at a time with a per-byte unsigned compare.
+constexpr int kValidateThreads = 224;       // a multiple of 7: a thread always sees the same word of a block
+__global__ void __launch_bounds__(kValidateThreads) validate_kernel(const uint32_t *__restrict__ words,
                                                        int64_t groups,
                                                        unsigned long long *__restrict__ counts) {
     unsigned bf = 0, bt = 0;
-    for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < groups;
-         g += (int64_t)gridDim.x * blockDim.x) {
-        const uint32_t *w = words + g * kBlockWords;
-        uint32_t w0 = w[0];
-        bf += ((w0 >> 16) & 0xffu) > kMaxFull;
-        bf += (w0 >> 24) > kMaxFull;
-#pragma unroll
-        for (int i = 1; i < 7; ++i) {
-            uint32_t v = w[i];
-            bf += (v & 0xffu) > kMaxFull;
-            bf += ((v >> 8) & 0xffu) > kMaxFull;
-            bf += ((v >> 16) & 0xffu) > kMaxFull;
-            if (i < 6) bf += (v >> 24) > kMaxFull;
-            else bt += (v >> 24) > kMaxTail;
-        }
+    const int64_t total = groups * kBlockWords;
+    // the grid stride is a multiple of 7 words, so the word's place in its block never changes
+    const int pos = threadIdx.x % kBlockWords;
+    const uint32_t full_mask = pos == 0 ? 0xffff0000u : pos == 6 ? 0x00ffffffu : 0xffffffffu;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t v = __ldg(words + i);
+        // 0xff in every byte that exceeds 242 (as unsigned bytes)
+        const uint32_t over = __vcmpgtu4(v, 0xf2f2f2f2u);
+        bf += __popc(over & full_mask) >> 3;
+        if (pos == 6) bt += (v >> 24) > kMaxTail;
     }
     for (int o = 16; o > 0; o >>= 1) {
         bf += __shfl_xor_sync(0xffffffffu, bf, o);
@@ -71,9 +71,9 @@ int launch_validate(const uint8_t *blocks, int64_t groups, int64_t *counts, cuda
     cudaError_t err = cudaMemsetAsync(counts, 0, 2 * sizeof(int64_t), stream);
     if (err != cudaSuccess) return cuda_fail(err, "tq1_validate_blocks_device: memset");
     if (groups == 0) return TQ1_OK;
-    int64_t ctas = (groups + 255) / 256;
+    int64_t ctas = (groups * kBlockWords + kValidateThreads - 1) / kValidateThreads;
     if (ctas > 148 * 8) ctas = 148 * 8;
-    validate_kernel<<<(unsigned)ctas, 256, 0, stream>>>(
+    validate_kernel<<<(unsigned)ctas, kValidateThreads, 0, stream>>>(
         reinterpret_cast<const uint32_t *>(blocks), groups,
         reinterpret_cast<unsigned long long *>(counts));
     err = cudaGetLastError();

@@ -232,3 +232,32 @@ def test_module_matches_kernel_and_keeps_leading_dims():
     bad[5, 2, 9] = 250
     with pytest.raises(ValueError, match="regular=1, tail=0"):
         lin.load_blocks(to_dev(bad))
+
+
+def test_device_byte_scan_counts_every_illegal_byte():
+    """The load-time scan on the device: exact counts of code bytes above 242 and tail bytes above 26,
+    whatever their place in the block, and a clean pass on legal data (scale bytes are never counted)."""
+    from ternel_b200 import FormatError
+    from ternel_b200.ops import validate_device_blocks
+    rows, columns = 1000, 1536
+    blocks, rng = random_blocks(rows, columns, seed=77)
+    blocks[:, :, 0:2] = 0xff                               # scale bytes may hold anything
+    dev = torch.from_numpy(blocks).cuda()
+    validate_device_blocks(dev)                            # legal: no exception
+    bad = blocks.copy().reshape(-1, 28)
+    picks = rng.choice(bad.shape[0], size=300, replace=False)
+    n_full = n_tail = 0
+    for n, g in enumerate(picks):
+        if n % 3 == 0:
+            bad[g, 27] = 27 + n % 200                      # tail byte above 26
+            n_tail += 1
+        else:
+            bad[g, 2 + n % 25] = 243 + n % 13              # a regular code byte above 242
+            n_full += 1
+            if n % 7 == 0:
+                bad[g, 2 + (n + 11) % 25] = 255
+                n_full += (n + 11) % 25 != n % 25
+    with pytest.raises(FormatError, match=f"regular={n_full}, tail={n_tail}"):
+        validate_device_blocks(torch.from_numpy(bad.reshape(blocks.shape)).cuda())
+    counts = torch.ops.ternel.tq1_validate(torch.from_numpy(bad.reshape(blocks.shape)).cuda()).cpu().tolist()
+    assert counts == [n_full, n_tail]
