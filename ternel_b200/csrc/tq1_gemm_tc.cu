@@ -289,6 +289,31 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         const bool whole = len == groups;
         float *slot = prm.partials + ((size_t)2 * blockIdx.x + (seg == 0 ? 0 : 1)) * (size_t)(NT * kTileW);
         const int n = n0 + r;
+        if (whole && prm.swiglu) {
+            // (gate, up) row pairs: the even row of a pair stores silu(gate) * up. Kept apart from the plain
+            // loop below, which is on the critical path of the large tiles.
+#pragma unroll 1
+            for (int c0 = 0; c0 < NT; c0 += 32) {
+                uint32_t v[32];
+                if (NT >= 32 || c0 == 0) {
+                    tmem_load32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + acc_col + (uint32_t)c0, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                }
+#pragma unroll 4
+                for (int c = 0; c < 32; ++c) {
+                    const int m = m0 + c0 + c;
+                    const float gate = __uint_as_float(v[c]);
+                    const float up = __shfl_down_sync(0xffffffffu, gate, 1);
+                    if (c0 + c < NT && m < prm.M && n + 1 < prm.N && (r & 1) == 0) {
+                        const float out = swiglu_f32(gate, up);
+                        const size_t o = (size_t)m * (prm.N >> 1) + (n >> 1);
+                        if (prm.y_f32) static_cast<float *>(prm.y)[o] = out;
+                        else static_cast<__half *>(prm.y)[o] = __float2half_rn(out);
+                    }
+                }
+            }
+            return;
+        }
 #pragma unroll 1
         for (int c0 = 0; c0 < NT; c0 += 32) {
             uint32_t v[32];
@@ -299,17 +324,6 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
                 const int m = m0 + c0 + c;
-                if (whole && prm.swiglu) {          // the even row of a (gate, up) pair stores the product
-                    const float gate = __uint_as_float(v[c]);
-                    const float up = __shfl_down_sync(0xffffffffu, gate, 1);
-                    if (c0 + c < NT && m < prm.M && n + 1 < prm.N && (r & 1) == 0) {
-                        const float out = swiglu_f32(gate, up);
-                        const size_t o = (size_t)m * (prm.N >> 1) + (n >> 1);
-                        if (prm.y_f32) static_cast<float *>(prm.y)[o] = out;
-                        else static_cast<__half *>(prm.y)[o] = __float2half_rn(out);
-                    }
-                    continue;
-                }
                 if (c0 + c < NT && m < prm.M && n < prm.N) {
                     const float f = __uint_as_float(v[c]);
                     if (!whole)
