@@ -221,6 +221,9 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     constexpr bool kEpi = gemm_epi_warps(NT, PERSIST);
     constexpr int kTmaWarp = kEpi ? 12 : 8, kMmaWarp = kEpi ? 13 : 9;
     constexpr int kAccBufs = kEpi ? 2 : 1;
+    // without epilogue warps, tiles of 64 tokens and more are stored by both decode groups, half the
+    // token columns each (the store is not overlapped with anything there)
+    constexpr bool kBothStore = !kEpi && NT >= 64;
     constexpr int kStagesG = gemm_stages(NT);
     constexpr int kPackBufs = gemm_pack_bufs(NT);
     constexpr int kBTileBytes = NT * kGroup * 2;
@@ -261,7 +264,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar(ACCUM + b), 1);
-            mbar_init(bar(ACC_FREE + b), 128);
+            mbar_init(bar(ACC_FREE + b), kBothStore ? 256 : 128);
         }
         mbar_init(bar(LUT_BAR), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -284,7 +287,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     // warp whose index modulo 4 names its 32 lanes). A segment that covers the tile's whole K range is
     // stored as the result; a partial one goes to this CTA's first- or last-segment slot as FP32 and is
     // added up by the fix-up kernel.
-    auto store_segment = [&](int seg, int len, int n0, int m0, uint32_t acc_col) {
+    auto store_segment = [&](int seg, int len, int n0, int m0, uint32_t acc_col, int c_begin, int c_end) {
         const int r = (warp & 3) * 32 + lane;
         const bool whole = len == groups;
         float *slot = prm.partials + ((size_t)2 * blockIdx.x + (seg == 0 ? 0 : 1)) * (size_t)(NT * kTileW);
@@ -293,7 +296,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             // (gate, up) row pairs: the even row of a pair stores silu(gate) * up. Kept apart from the plain
             // loop below, which is on the critical path of the large tiles.
 #pragma unroll 1
-            for (int c0 = 0; c0 < NT; c0 += 32) {
+            for (int c0 = c_begin; c0 < c_end; c0 += 32) {
                 uint32_t v[32];
                 if (NT >= 32 || c0 == 0) {
                     tmem_load32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + acc_col + (uint32_t)c0, v);
@@ -315,7 +318,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             return;
         }
 #pragma unroll 1
-        for (int c0 = 0; c0 < NT; c0 += 32) {
+        for (int c0 = c_begin; c0 < c_end; c0 += 32) {
             uint32_t v[32];
             if (NT >= 32 || c0 == 0) {
                 tmem_load32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + acc_col + (uint32_t)c0, v);
@@ -418,7 +421,8 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             ok = mbar_wait(bar(ACCUM + buf), (uint32_t)use & 1u, prm.status);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            store_segment(seg, len, (tile / prm.tiles_m) * kTileW, (tile % prm.tiles_m) * NT, (uint32_t)(buf * kAccCols));
+            store_segment(seg, len, (tile / prm.tiles_m) * kTileW, (tile % prm.tiles_m) * NT, (uint32_t)(buf * kAccCols),
+                          0, NT);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(bar(ACC_FREE + buf));
             it += len;
@@ -508,11 +512,13 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             if (last_of_chunk) mbar_arrive(bar(PACK_EMPTY + pack_i % kPackBufs));
         }
 
-        if (!kEpi) {         // the first decode group also stores the segment's result
-            if (ok && group == 0) ok = mbar_wait(bar(ACCUM), (uint32_t)seg & 1u, prm.status);
-            if (ok && group == 0) {
+        if (!kEpi) {         // the decode warps also store the segment's result
+            const bool storing = kBothStore || group == 0;
+            if (ok && storing) ok = mbar_wait(bar(ACCUM), (uint32_t)seg & 1u, prm.status);
+            if (ok && storing) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                store_segment(seg, len, n0, m0, 0u);
+                if (kBothStore) store_segment(seg, len, n0, m0, 0u, group * (NT / 2), (group + 1) * (NT / 2));
+                else store_segment(seg, len, n0, m0, 0u, 0, NT);
                 // the accumulator columns may be overwritten by the next segment
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 mbar_arrive(bar(ACC_FREE));
