@@ -671,8 +671,8 @@ int token_tile(int M, int N, int K) {
     if (g_forced_tile) return g_forced_tile;
     if (M <= 16) return 16;
     static const int tiles[5] = {16, 32, 64, 128, 256};
-    static const float per_block_us[5] = {0.8f, 0.55f, 0.55f, 0.7f, 1.1f};
-    static const float per_store_us[5] = {0.0f, 1.0f, 2.0f, 2.0f, 12.0f};
+    static const float per_block_us[5] = {0.85f, 0.5f, 0.55f, 0.8f, 0.8f};
+    static const float per_store_us[5] = {0.0f, 1.0f, 1.0f, 0.0f, 2.0f};
     int best = 128;
     float best_cost = 0.0f;
     for (int i = 0; i < 5; ++i) {
