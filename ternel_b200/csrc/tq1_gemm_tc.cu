@@ -190,6 +190,10 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
 struct WorkSplit {
     int total_iters, ctas, groups, splits;      // splits == 0: equal contiguous ranges
     int quot, rem;                              // total_iters = ctas * quot + rem: the first `rem` ranges get one more
+    // Stream-K mode only: every CTA first computes `whole_rounds` whole tiles (tiles cta * whole_rounds + k),
+    // and only the remaining tiles, numbered from whole_tiles on, are cut into ranges (total_iters counts
+    // their iterations). Whole tiles need neither a partial store nor the fix-up.
+    int whole_rounds, whole_tiles;
     __host__ __device__ int first_iter(int cta) const {
         if (cta >= ctas) return total_iters;
         if (splits == 0) return cta * quot + (cta < rem ? cta : rem);
@@ -214,6 +218,32 @@ struct GemmParams {
 
 // PERSIST = false: the CTA's range is known to be one segment (the equal-parts split), and the
 // segment loops below compile to straight-line code.
+// A CTA's segments in order: its whole tiles, then the pieces of its range of the shared tiles.
+struct SegmentWalk {
+    const WorkSplit &w;
+    int cta, round, it, end, pieces;
+    __device__ SegmentWalk(const WorkSplit &work, int cta_)
+        : w(work), cta(cta_), round(0), it(work.first_iter(cta_)), end(work.first_iter(cta_ + 1)), pieces(0) {}
+    // slot: which of the CTA's two partial-tile slots a partial segment is stored to
+    __device__ bool next(int &tile, int &kb0, int &len, int &slot) {
+        if (round < w.whole_rounds) {
+            tile = cta * w.whole_rounds + round++;
+            kb0 = 0;
+            len = w.groups;
+            slot = 0;
+            return true;
+        }
+        if (it >= end) return false;
+        const int t = it / w.groups;
+        kb0 = it - t * w.groups;
+        len = min(w.groups - kb0, end - it);
+        tile = w.whole_tiles + t;
+        slot = pieces++ == 0 ? 0 : 1;
+        it += len;
+        return true;
+    }
+};
+
 template <int NT, bool PERSIST>
 __global__ void __launch_bounds__(gemm_threads(NT, PERSIST), NT <= 16 ? 2 : 1)
 tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
@@ -249,8 +279,6 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
     const int groups = prm.K / kGroup;
-    const int it_begin = prm.work.first_iter(blockIdx.x);
-    const int it_end = prm.work.first_iter(blockIdx.x + 1);
 
     if (tid == 0) {
         for (int s = 0; s < kStagesG; ++s) {
@@ -287,10 +315,10 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     // warp whose index modulo 4 names its 32 lanes). A segment that covers the tile's whole K range is
     // stored as the result; a partial one goes to this CTA's first- or last-segment slot as FP32 and is
     // added up by the fix-up kernel.
-    auto store_segment = [&](int seg, int len, int n0, int m0, uint32_t acc_col, int c_begin, int c_end) {
+    auto store_segment = [&](int which, int len, int n0, int m0, uint32_t acc_col, int c_begin, int c_end) {
         const int r = (warp & 3) * 32 + lane;
         const bool whole = len == groups;
-        float *slot = prm.partials + ((size_t)2 * blockIdx.x + (seg == 0 ? 0 : 1)) * (size_t)(NT * kTileW);
+        float *slot = prm.partials + ((size_t)2 * blockIdx.x + which) * (size_t)(NT * kTileW);
         const int n = n0 + r;
         if (whole && prm.swiglu) {
             // (gate, up) row pairs: the even row of a pair stores silu(gate) * up. Kept apart from the plain
@@ -344,10 +372,10 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         // lane 1 keeps the queue of packed-byte chunks full, lane 0 feeds the activation tiles;
         // the two run independently so that the weight prefetch can run several chunks ahead
         if (lane == 1) {
-            int pack_i = 0, it = it_begin;
+            int pack_i = 0, tile, kb0, len, which;
+            SegmentWalk walk(prm.work, blockIdx.x);
+            bool more = walk.next(tile, kb0, len, which);
             do {
-                const int tile = it / groups, kb0 = it - tile * groups;
-                const int len = min(groups - kb0, it_end - it);
                 const int n0 = (tile / prm.tiles_m) * kTileW;
                 const int first_chunk = kb0 / kPackGroups, last_chunk = (kb0 + len - 1) / kPackGroups;
                 for (int c = first_chunk; c <= last_chunk && ok; ++c, ++pack_i) {
@@ -358,13 +386,13 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     tma_load_2d((uint32_t)__cvta_generic_to_shared(packed + p * kPackBytes), &wmap,
                                 c * (kPackGroups * kBlockBytes), n0, bar(PACK_FULL + p));
                 }
-                it += len;
-            } while (PERSIST && it < it_end && ok);
+                more = walk.next(tile, kb0, len, which);
+            } while (PERSIST && more && ok);
         } else if (lane == 0) {
-            int i = 0, it = it_begin;
+            int i = 0, tile, kb0, len, which;
+            SegmentWalk walk(prm.work, blockIdx.x);
+            bool more = walk.next(tile, kb0, len, which);
             do {
-                const int tile = it / groups, kb0 = it - tile * groups;
-                const int len = min(groups - kb0, it_end - it);
                 const int m0 = (tile % prm.tiles_m) * NT;
                 for (int kb = kb0; kb < kb0 + len && ok; ++kb, ++i) {
                     const int s = i % kStagesG;
@@ -375,18 +403,18 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     tma_load_2d(dst, &xmap, kb * kGroup, m0, bar(FULL_B + s));
                     tma_load_2d(dst + NT * 128, &xmap, kb * kGroup + 64, m0, bar(FULL_B + s));
                 }
-                it += len;
-            } while (PERSIST && it < it_end && ok);
+                more = walk.next(tile, kb0, len, which);
+            } while (PERSIST && more && ok);
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             // instruction descriptor: FP32 accumulate, FP16 A and B, both K-major, M = 128, N = NT
             const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(kTileW >> 4) << 24);
-            int i = 0, seg = 0, it = it_begin;
+            int i = 0, seg = 0, tile, kb0, len, which;
+            SegmentWalk walk(prm.work, blockIdx.x);
+            bool more = walk.next(tile, kb0, len, which);
             do {
-                const int tile = it / groups, kb0 = it - tile * groups;
-                const int len = min(groups - kb0, it_end - it);
                 // the accumulator's previous contents must have been read out
                 const int buf = seg % kAccBufs, use = seg / kAccBufs;
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kAccCols);
@@ -407,27 +435,27 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     umma_commit(bar(EMPTY + s));            // the stage is free once these MMAs have read it
                 }
                 if (ok) umma_commit(bar(ACCUM + buf));      // the segment's accumulator is complete
-                it += len;
                 ++seg;
-            } while (PERSIST && it < it_end && ok);
+                more = walk.next(tile, kb0, len, which);
+            } while (PERSIST && more && ok);
         }
     } else if (kEpi && warp >= 8) {
         // ------------------------------------------------------------------ epilogue warps 8-11
-        int seg = 0, it = it_begin;
+        int seg = 0, tile, kb0, len, which;
+        SegmentWalk walk(prm.work, blockIdx.x);
+        bool more = walk.next(tile, kb0, len, which);
         do {
-            const int tile = it / groups, kb0 = it - tile * groups;
-            const int len = min(groups - kb0, it_end - it);
             const int buf = seg % kAccBufs, use = seg / kAccBufs;
             ok = mbar_wait(bar(ACCUM + buf), (uint32_t)use & 1u, prm.status);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            store_segment(seg, len, (tile / prm.tiles_m) * kTileW, (tile % prm.tiles_m) * NT, (uint32_t)(buf * kAccCols),
-                          0, NT);
+            store_segment(which, len, (tile / prm.tiles_m) * kTileW, (tile % prm.tiles_m) * NT,
+                          (uint32_t)(buf * kAccCols), 0, NT);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(bar(ACC_FREE + buf));
-            it += len;
             ++seg;
-        } while (it < it_end);
+            more = walk.next(tile, kb0, len, which);
+        } while (more);
     } else {
         // ------------------------------------------------------------------ decode (thread = weight row)
         // two groups of four warps take alternate K blocks, so two stages are being filled at a time
@@ -435,10 +463,10 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         const int r = (warp & 3) * 32 + lane;            // 0..127 = tensor-memory lane (a warp reaches lanes 32*(warp%4)..)
         ok = mbar_wait(bar(LUT_BAR), 0, prm.status);
         const uint32_t lut_lane = (uint32_t)__cvta_generic_to_shared(lut) + (uint32_t)lane * 8u;
-        int pack_i = -1, i = 0, seg = 0, it = it_begin;
+        int pack_i = -1, i = 0, seg = 0, tile, kb0, len, which;
+        SegmentWalk walk(prm.work, blockIdx.x);
+        bool more = walk.next(tile, kb0, len, which);
         do {
-        const int tile = it / groups, kb0 = it - tile * groups;
-        const int len = min(groups - kb0, it_end - it);
         const int n0 = (tile / prm.tiles_m) * kTileW;       // first weight row of the tile
         const int m0 = (tile % prm.tiles_m) * NT;           // first activation row
         for (int ii = 0; ii < len && ok; ++ii, ++i) {
@@ -517,16 +545,16 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             if (ok && storing) ok = mbar_wait(bar(ACCUM), (uint32_t)seg & 1u, prm.status);
             if (ok && storing) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (kBothStore) store_segment(seg, len, n0, m0, 0u, group * (NT / 2), (group + 1) * (NT / 2));
-                else store_segment(seg, len, n0, m0, 0u, 0, NT);
+                if (kBothStore) store_segment(which, len, n0, m0, 0u, group * (NT / 2), (group + 1) * (NT / 2));
+                else store_segment(which, len, n0, m0, 0u, 0, NT);
                 // the accumulator columns may be overwritten by the next segment
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 mbar_arrive(bar(ACC_FREE));
             }
         }
-        it += len;
         ++seg;
-        } while (PERSIST && it < it_end && ok);   // segments
+        more = walk.next(tile, kb0, len, which);
+        } while (PERSIST && more && ok);   // segments
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -564,15 +592,16 @@ tq1_streamk_fixup_kernel(const float *__restrict__ partials, void *__restrict__ 
         c_lo = blockIdx.x;                                             // the CTA before the boundary
         const int it_b = work.first_iter(c_lo + 1);
         if (it_b % groups == 0) return;                                // the boundary falls between two tiles
-        tile = it_b / groups;
+        tile = it_b / groups;                                          // among the shared tiles
         it0 = tile * groups;
         if (work.first_iter(c_lo) > it0) return;                       // an earlier boundary lies in this tile
         c_hi = c_lo + 1;
         while (c_hi + 1 < ctas && work.first_iter(c_hi + 1) < it0 + groups) ++c_hi;
     }
     const int r = threadIdx.x;
-    const int n = (tile / tiles_m) * kTileW + r;
-    const int m0 = (tile % tiles_m) * nt;
+    const int out_tile = work.splits > 0 ? tile : work.whole_tiles + tile;
+    const int n = (out_tile / tiles_m) * kTileW + r;
+    const int m0 = (out_tile % tiles_m) * nt;
     const int c0 = blockIdx.y * kFixCols;
     const bool live = n < N;
     float total[kFixCols];
@@ -644,9 +673,21 @@ WorkSplit split_work(int nt, int M, int N, int K) {
     WorkSplit w;
     w.groups = K / kGroup;
     w.total_iters = (int)(tiles * w.groups);
+    w.whole_rounds = w.whole_tiles = 0;
     if (tiles >= slots) {
         w.splits = 0;
         w.ctas = (int)slots;
+        // whole tiles first; what is left over is shared. A share of fewer than eight K blocks per CTA
+        // would cost more in partial stores than it balances, so then one round of whole tiles is shared too.
+        long long rounds = tiles / slots;
+        long long shared = tiles - rounds * slots;
+        if (shared > 0 && shared * w.groups < 8 * slots) {
+            --rounds;
+            shared += slots;
+        }
+        w.whole_rounds = (int)rounds;
+        w.whole_tiles = (int)(rounds * slots);
+        w.total_iters = (int)(shared * w.groups);
     } else {
         int splits = (int)(slots / tiles);
         const int max_splits = w.groups / 8 > 0 ? w.groups / 8 : 1;
@@ -679,8 +720,11 @@ int token_tile(int M, int N, int K) {
         const int nt = tiles[i];
         if (nt > 16 && nt >= 4 * M) continue;           // a tile mostly of padding
         const WorkSplit w = split_work(nt, M, N, K);
-        const float blocks = w.splits ? (float)((w.groups + w.splits - 1) / w.splits) : (float)w.total_iters / w.ctas;
-        const float stores = w.splits ? 1.0f : blocks / w.groups + 1.0f;
+        const float shared = (float)w.total_iters / w.ctas;           // K blocks of shared tiles per CTA
+        const float blocks = w.splits ? (float)((w.groups + w.splits - 1) / w.splits)
+                                      : (float)w.whole_rounds * w.groups + shared;
+        const float stores = w.splits ? 1.0f
+                                      : (float)w.whole_rounds + (w.total_iters ? shared / w.groups + 1.0f : 0.0f);
         const float cost = blocks * per_block_us[i] + stores * per_store_us[i];
         if (i == 0 || cost < best_cost) { best = nt; best_cost = cost; }
     }
@@ -812,7 +856,8 @@ int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, 
            : nt == 128 ? launch_nt<128, true>(wmap, xmap, prm, grid, stream)
                        : launch_nt<256, true>(wmap, xmap, prm, grid, stream);
     if (rc != TQ1_OK) return rc;
-    const bool shared_tiles = work.splits > 1 || (work.splits == 0 && (work.rem != 0 || work.quot % work.groups != 0));
+    const bool shared_tiles = work.splits > 1 || (work.splits == 0 && work.total_iters > 0 &&
+                                                  (work.rem != 0 || work.quot % work.groups != 0));
     if (ctas > 1 && shared_tiles) {
         const unsigned fix_blocks = work.splits > 0 ? (unsigned)(ctas / work.splits) : (unsigned)(ctas - 1);
         const unsigned col_blocks = (unsigned)(((M < nt ? M : nt) + kFixCols - 1) / kFixCols);
