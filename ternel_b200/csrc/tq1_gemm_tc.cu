@@ -9,12 +9,13 @@
 //
 // An output tile is 128 weight rows x NT activation rows:
 //   D[n][m] = sum_k W[n][k] * x[m][k]      (A = W tile, B = x tile, both K-major FP16)
-// Persistent CTAs (one per SM, two for the 16-token tiles) share the work stream-K fashion: the
-// (tile, K block) iterations, numbered tile-major, are cut into equal contiguous ranges, so every CTA
-// does the same number of K blocks whatever the tile count. A range is a sequence of segments; a
-// segment that covers a tile's whole K range is stored as the result, a partial one (only a CTA's
-// first or last) goes to the workspace as FP32 and a fix-up kernel adds the pieces of such a tile
-// in ascending K order (deterministic).
+// Persistent CTAs (one per SM, two for the 16-token tiles). Every CTA first computes the same number
+// of whole tiles; the leftover tiles are shared stream-K fashion: their (tile, K block) iterations,
+// numbered tile-major, are cut into equal contiguous ranges, so every CTA does the same number of K
+// blocks whatever the tile count. A range is a sequence of segments; a segment that covers a tile's
+// whole K range is stored as the result, a partial one (only the first or last of a CTA's range) goes
+// to the workspace as FP32 and a fix-up kernel adds the pieces of such a tile in ascending K order
+// (deterministic).
 //   warps 0-3, 4-7  decode: thread r of a group turns row r's 28-byte block into 128 FP16 values
 //              and stores them with tcgen05.st into lane r of tensor memory, where the MMA reads
 //              its A operand (the weights never pass through shared memory); the two groups take
