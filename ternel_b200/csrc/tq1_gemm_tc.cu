@@ -46,7 +46,6 @@ namespace {
 constexpr int kTileW = 128;                 // weight rows per tile (UMMA M)
 constexpr int kPackGroups = 4;
 constexpr int kPackBytes = kTileW * kPackGroups * kBlockBytes;     // 14336
-constexpr int kLutBytesG = 243 * 256;                              // 8-byte entries x 32 lanes
 // Warp roles. Plain variant (320 threads): warps 0-3 and 4-7 decode, warp 8 TMA, warp 9 MMA, and the first
 // decode group also stores the results. Variant with epilogue warps (448 threads, persistent kernel with
 // 32- to 128-token tiles): warps 8-11 store the results out of a second accumulator while the MMA warp is
@@ -56,7 +55,11 @@ __host__ __device__ constexpr int gemm_threads(int nt, bool persist) { return ge
 constexpr int kAStageCols = kGroup / 2;      // a 128-wide K block of FP16 weights = 64 tensor-memory columns
 // Small activation tiles: three stages and little shared memory, so that two CTAs share an SM and
 // hide each other's latencies. Large tiles: one CTA per SM with as many stages as fit.
-__host__ __device__ constexpr int gemm_stages(int nt) { return nt > 128 ? 2 : nt <= 16 ? 3 : 4; }
+__host__ __device__ constexpr int gemm_stages(int nt) { return nt > 128 ? 3 : nt <= 16 ? 3 : 4; }
+// The decode table is replicated per lane (8-byte entries x 32 lanes, conflict-free) except for the
+// 256-token tile: there the tensor cores set the pace, the lookups' bank conflicts are hidden, and
+// the 60 KB saved by a single copy of the table pay for a third 64 KB activation stage.
+__host__ __device__ constexpr int gemm_lut_bytes(int nt) { return nt > 128 ? 2048 : 243 * 256; }
 __host__ __device__ constexpr int gemm_tmem_cols(int nt) { return nt <= 16 ? 256 : 512; }
 // packed-byte buffers (4 K blocks each): small activation tiles leave room for a deep prefetch queue,
 // which is what hides HBM latency when the tensor work per K block is tiny
@@ -92,6 +95,14 @@ constexpr GemmLutImage make_gemm_lut() {
     return img;
 }
 __device__ __align__(128) const GemmLutImage g_gemm_lut = make_gemm_lut();
+struct GemmLutSmall { uint32_t w[512]; };
+constexpr GemmLutSmall make_gemm_lut_small() {
+    GemmLutSmall img{};
+    const GemmLutImage big = make_gemm_lut();
+    for (int v = 0; v < 243; ++v) { img.w[2 * v] = big.w[v * 64]; img.w[2 * v + 1] = big.w[v * 64 + 1]; }
+    return img;
+}
+__device__ __align__(128) const GemmLutSmall g_gemm_lut_small = make_gemm_lut_small();
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t d;
@@ -268,7 +279,8 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     unsigned char *b_tiles = smem;                                       // kStagesG x NT*256, 1024-aligned
     unsigned char *packed = b_tiles + kStagesG * kBTileBytes;            // 2 x 14336
     unsigned char *lut = packed + kPackBufs * kPackBytes;                // 62208
-    uint64_t *bars = reinterpret_cast<uint64_t *>(lut + kLutBytesG);
+    constexpr int kLutBytes = gemm_lut_bytes(NT);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(lut + kLutBytes);
     // barrier indices
     constexpr int FULL_A = 0, FULL_B = FULL_A + kStagesG, EMPTY = FULL_B + kStagesG, PACK_FULL = EMPTY + kStagesG,
                   PACK_EMPTY = PACK_FULL + kPackBufs, ACCUM = PACK_EMPTY + kPackBufs, ACC_FREE = ACCUM + 2,
@@ -298,8 +310,11 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         mbar_init(bar(LUT_BAR), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_expect_tx(bar(LUT_BAR), kLutBytesG);
-        bulk_load((uint32_t)__cvta_generic_to_shared(lut), &g_gemm_lut, kLutBytesG, bar(LUT_BAR));
+        mbar_expect_tx(bar(LUT_BAR), kLutBytes);
+        if (kLutBytes == 2048)
+            bulk_load((uint32_t)__cvta_generic_to_shared(lut), &g_gemm_lut_small, kLutBytes, bar(LUT_BAR));
+        else
+            bulk_load((uint32_t)__cvta_generic_to_shared(lut), &g_gemm_lut, kLutBytes, bar(LUT_BAR));
     }
     if (warp == kMmaWarp) {        // tensor-memory allocation is a warp-wide operation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -463,7 +478,8 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         const int group = warp < 4 ? 0 : 1;
         const int r = (warp & 3) * 32 + lane;            // 0..127 = tensor-memory lane (a warp reaches lanes 32*(warp%4)..)
         ok = mbar_wait(bar(LUT_BAR), 0, prm.status);
-        const uint32_t lut_lane = (uint32_t)__cvta_generic_to_shared(lut) + (uint32_t)lane * 8u;
+        const uint32_t lut_lane = (uint32_t)__cvta_generic_to_shared(lut) + (kLutBytes == 2048 ? 0u : (uint32_t)lane * 8u);
+        constexpr int kLutShift = kLutBytes == 2048 ? 3 : 8;
         int pack_i = -1, i = 0, seg = 0, tile, kb0, len, which;
         SegmentWalk walk(prm.work, blockIdx.x);
         bool more = walk.next(tile, kb0, len, which);
@@ -499,7 +515,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             for (int j = 0; j < 26; ++j) {
                 const int bytepos = 2 + j;
                 const uint32_t byte = (w[bytepos >> 2] >> (8 * (bytepos & 3))) & 0xffu;
-                const uint32_t addr = lut_lane + (byte << 8);
+                const uint32_t addr = lut_lane + (byte << kLutShift);
                 asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(e0[j]), "=r"(e1[j]) : "r"(addr));
             }
             // 64 registers = the row's 128 FP16 weights in decode order, written to this lane of tensor memory
@@ -742,7 +758,7 @@ size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 template <int NT>
 size_t gemm_smem_bytes() {
     return (size_t)gemm_stages(NT) * NT * kGroup * 2 +
-           (size_t)gemm_pack_bufs(NT) * kPackBytes + kLutBytesG + 512 + 1024;
+           (size_t)gemm_pack_bufs(NT) * kPackBytes + gemm_lut_bytes(NT) + 512 + 1024;
 }
 
 template <int NT, bool PERSIST>
