@@ -206,7 +206,7 @@ struct WorkSplit {
     // and only the remaining tiles, numbered from whole_tiles on, are cut into ranges (total_iters counts
     // their iterations). Whole tiles need neither a partial store nor the fix-up.
     int whole_rounds, whole_tiles;
-    __host__ __device__ int first_iter(int cta) const {
+    __host__ __device__ __forceinline__ int first_iter(int cta) const {
         if (cta >= ctas) return total_iters;
         if (splits == 0) return cta * quot + (cta < rem ? cta : rem);
         const int tile = cta / splits, part = cta - tile * splits;
@@ -230,26 +230,28 @@ struct GemmParams {
 
 // PERSIST = false: the CTA's range is known to be one segment (the equal-parts split), and the
 // segment loops below compile to straight-line code.
-// A CTA's segments in order: its whole tiles, then the pieces of its range of the shared tiles.
+// A CTA's segments in order: its whole tiles, then the pieces of its range of the shared tiles. Holds
+// copies of the few numbers it needs: a reference to the kernel parameter would force the whole
+// parameter block into local memory.
 struct SegmentWalk {
-    const WorkSplit &w;
-    int cta, round, it, end, pieces;
-    __device__ SegmentWalk(const WorkSplit &work, int cta_)
-        : w(work), cta(cta_), round(0), it(work.first_iter(cta_)), end(work.first_iter(cta_ + 1)), pieces(0) {}
+    int groups, whole_rounds, whole_tiles, cta, round, it, end, pieces;
+    __device__ __forceinline__ SegmentWalk(const WorkSplit work, int cta_)
+        : groups(work.groups), whole_rounds(work.whole_rounds), whole_tiles(work.whole_tiles), cta(cta_), round(0),
+          it(work.first_iter(cta_)), end(work.first_iter(cta_ + 1)), pieces(0) {}
     // slot: which of the CTA's two partial-tile slots a partial segment is stored to
-    __device__ bool next(int &tile, int &kb0, int &len, int &slot) {
-        if (round < w.whole_rounds) {
-            tile = cta * w.whole_rounds + round++;
+    __device__ __forceinline__ bool next(int &tile, int &kb0, int &len, int &slot) {
+        if (round < whole_rounds) {
+            tile = cta * whole_rounds + round++;
             kb0 = 0;
-            len = w.groups;
+            len = groups;
             slot = 0;
             return true;
         }
         if (it >= end) return false;
-        const int t = it / w.groups;
-        kb0 = it - t * w.groups;
-        len = min(w.groups - kb0, end - it);
-        tile = w.whole_tiles + t;
+        const int t = it / groups;
+        kb0 = it - t * groups;
+        len = min(groups - kb0, end - it);
+        tile = whole_tiles + t;
         slot = pieces++ == 0 ? 0 : 1;
         it += len;
         return true;
@@ -292,6 +294,18 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
     const int groups = prm.K / kGroup;
+    // Without the persistent loop the CTA's range is one piece of one tile; it is worked out here once,
+    // so that the walker and the loops around the segments compile away.
+    const int only_begin = PERSIST ? 0 : prm.work.first_iter(blockIdx.x);
+    const int only_end = PERSIST ? 0 : prm.work.first_iter(blockIdx.x + 1);
+    auto first_segment = [&](SegmentWalk &walk, int &tile, int &kb0, int &len, int &slot) -> bool {
+        if (PERSIST) return walk.next(tile, kb0, len, slot);
+        tile = only_begin / groups;
+        kb0 = only_begin - tile * groups;
+        len = only_end - only_begin;
+        slot = 0;
+        return false;
+    };
 
     if (tid == 0) {
         for (int s = 0; s < kStagesG; ++s) {
@@ -390,7 +404,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         if (lane == 1) {
             int pack_i = 0, tile, kb0, len, which;
             SegmentWalk walk(prm.work, blockIdx.x);
-            bool more = walk.next(tile, kb0, len, which);
+            bool more = first_segment(walk, tile, kb0, len, which);
             do {
                 const int n0 = (tile / prm.tiles_m) * kTileW;
                 const int first_chunk = kb0 / kPackGroups, last_chunk = (kb0 + len - 1) / kPackGroups;
@@ -402,12 +416,12 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     tma_load_2d((uint32_t)__cvta_generic_to_shared(packed + p * kPackBytes), &wmap,
                                 c * (kPackGroups * kBlockBytes), n0, bar(PACK_FULL + p));
                 }
-                more = walk.next(tile, kb0, len, which);
+                if (PERSIST) more = walk.next(tile, kb0, len, which);
             } while (PERSIST && more && ok);
         } else if (lane == 0) {
             int i = 0, tile, kb0, len, which;
             SegmentWalk walk(prm.work, blockIdx.x);
-            bool more = walk.next(tile, kb0, len, which);
+            bool more = first_segment(walk, tile, kb0, len, which);
             do {
                 const int m0 = (tile % prm.tiles_m) * NT;
                 for (int kb = kb0; kb < kb0 + len && ok; ++kb, ++i) {
@@ -419,7 +433,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     tma_load_2d(dst, &xmap, kb * kGroup, m0, bar(FULL_B + s));
                     tma_load_2d(dst + NT * 128, &xmap, kb * kGroup + 64, m0, bar(FULL_B + s));
                 }
-                more = walk.next(tile, kb0, len, which);
+                if (PERSIST) more = walk.next(tile, kb0, len, which);
             } while (PERSIST && more && ok);
         }
     } else if (warp == kMmaWarp) {
@@ -429,7 +443,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(kTileW >> 4) << 24);
             int i = 0, seg = 0, tile, kb0, len, which;
             SegmentWalk walk(prm.work, blockIdx.x);
-            bool more = walk.next(tile, kb0, len, which);
+            bool more = first_segment(walk, tile, kb0, len, which);
             do {
                 // the accumulator's previous contents must have been read out
                 const int buf = seg % kAccBufs, use = seg / kAccBufs;
@@ -452,14 +466,14 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 }
                 if (ok) umma_commit(bar(ACCUM + buf));      // the segment's accumulator is complete
                 ++seg;
-                more = walk.next(tile, kb0, len, which);
+                if (PERSIST) more = walk.next(tile, kb0, len, which);
             } while (PERSIST && more && ok);
         }
     } else if (kEpi && warp >= 8) {
         // ------------------------------------------------------------------ epilogue warps 8-11
         int seg = 0, tile, kb0, len, which;
         SegmentWalk walk(prm.work, blockIdx.x);
-        bool more = walk.next(tile, kb0, len, which);
+        bool more = first_segment(walk, tile, kb0, len, which);
         do {
             const int buf = seg % kAccBufs, use = seg / kAccBufs;
             ok = mbar_wait(bar(ACCUM + buf), (uint32_t)use & 1u, prm.status);
@@ -470,7 +484,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(bar(ACC_FREE + buf));
             ++seg;
-            more = walk.next(tile, kb0, len, which);
+            if (PERSIST) more = walk.next(tile, kb0, len, which);
         } while (more);
     } else {
         // ------------------------------------------------------------------ decode (thread = weight row)
@@ -482,7 +496,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         constexpr int kLutShift = kLutBytes == 2048 ? 3 : 8;
         int pack_i = -1, i = 0, seg = 0, tile, kb0, len, which;
         SegmentWalk walk(prm.work, blockIdx.x);
-        bool more = walk.next(tile, kb0, len, which);
+        bool more = first_segment(walk, tile, kb0, len, which);
         do {
         const int n0 = (tile / prm.tiles_m) * kTileW;       // first weight row of the tile
         const int m0 = (tile % prm.tiles_m) * NT;           // first activation row
@@ -570,7 +584,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             }
         }
         ++seg;
-        more = walk.next(tile, kb0, len, which);
+        if (PERSIST) more = walk.next(tile, kb0, len, which);
         } while (PERSIST && more && ok);   // segments
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
