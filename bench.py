@@ -354,8 +354,9 @@ def run_gpu_arm(args) -> None:
 
 
 def measure_shapes(stack, device, replays: int = 5):
-    """Stream regime per projection shape: the same projection of every layer back to back
-    (distinct weight buffers, far more than L2 in total), one CUDA graph per shape."""
+    """Per projection shape, one CUDA graph of back-to-back launches: the stream regime (the same
+    projection of every layer, distinct weight buffers, far more than L2 in total: the HBM number) and the
+    warm regime (one buffer repeatedly: L2-resident weights). The chained regime is the step itself."""
     import ctypes
     import torch
     from ternel_b200.format import check
@@ -368,34 +369,41 @@ def measure_shapes(stack, device, replays: int = 5):
             continue
         seen.add((n, k))
 
-        def run():
-            stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
-            for layer in stack.weights:
-                check(lib.tq1_linear_f16(layer[j].data_ptr(), stack.inputs[k].data_ptr(),
-                                         stack.outputs[n].data_ptr(), 0, stack.batch, n, k,
-                                         stack.workspace.data_ptr(), stack.workspace_bytes, stream))
+        def timed(same_buffer: bool) -> float:
+            """us per launch of one CUDA graph holding len(stack.weights) launches of this shape."""
+            def run():
+                stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+                for layer in stack.weights:
+                    blocks = stack.weights[0][j] if same_buffer else layer[j]
+                    check(lib.tq1_linear_f16(blocks.data_ptr(), stack.inputs[k].data_ptr(),
+                                             stack.outputs[n].data_ptr(), 0, stack.batch, n, k,
+                                             stack.workspace.data_ptr(), stack.workspace_bytes, stream))
 
-        side = torch.cuda.Stream(device=device)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            run()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            run()
-        for _ in range(2):
-            graph.replay()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        start.record()
-        for _ in range(replays):
-            graph.replay()
-        stop.record()
-        torch.cuda.synchronize()
-        us = start.elapsed_time(stop) * 1e3 / (replays * len(stack.weights))
+            side = torch.cuda.Stream(device=device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                run()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                run()
+            for _ in range(2):
+                graph.replay()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(replays):
+                graph.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            return start.elapsed_time(stop) * 1e3 / (replays * len(stack.weights))
+
+        us = timed(False)           # stream regime: distinct buffers, HBM
+        warm = timed(True)          # warm regime: one buffer over and over, L2
         alg = n * k // 128 * 28 + 2 * stack.batch * (n + k)
-        out[f"{n}x{k}"] = {"us_per_launch": us, "gbps": alg / us / 1e3, "ring_buffers": len(stack.weights)}
+        out[f"{n}x{k}"] = {"us_per_launch": us, "gbps": alg / us / 1e3, "ring_buffers": len(stack.weights),
+                           "warm_l2_us_per_launch": warm, "warm_l2_gbps": alg / warm / 1e3}
     return out
 
 
