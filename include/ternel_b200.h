@@ -100,13 +100,14 @@ size_t tq1_linear_workspace_bytes(int M, int N, int K);
  *             aligned (may be NULL when that is 0). It must be zero-filled
  *             once before its first use; every call leaves it ready for the
  *             next one, of any shape. Calls that may overlap on the GPU
- *             (different streams) need separate workspaces. Layout: status
+ *             (different streams) need separate workspaces. Layout: control
  *             words (256 B; word 0 becomes non-zero if a bounded wait inside
- *             a kernel ran out), then 16 MiB of partial-sum slots for M == 1
- *             (eight bytes per row and 512-wide K chunk: the value and a
- *             "present" flag in one 64-bit word, cleared again by the call
- *             that used them), then the scratch of the M >= 2 kernels. After
- *             a non-zero status, zero-fill the workspace again.
+ *             a kernel ran out, words 1..4 are counters of the M == 1 kernel),
+ *             then 16 MiB of partial-sum slots for M == 1 (eight bytes per row
+ *             and 512-wide K chunk: the value and a sequence tag in one 64-bit
+ *             word, so nothing is ever cleared), then the scratch of the
+ *             M >= 2 kernels. After a non-zero status, zero-fill the workspace
+ *             again.
  * The kernel is chosen from M: 1 => streaming GEMV, 2..16 => small-batch
  * split-K GEMV, larger => tiled GEMM. Illegal code bytes must have been
  * rejected at load (tq1_validate_blocks*): the kernels carry no clamp. */
@@ -179,7 +180,7 @@ int tq1_linear_f16_sharded(const uint8_t *blocks, const void *x, const tq1_shard
  * reference: it exists for hosts that must not allocate at call time -- code running inside a
  * stream-capture region (cudaMalloc is illegal there), plugin hosts whose device budget was
  * fixed when the model was loaded, real-time loops that stay away from the allocator.
- * Same arithmetic and result as tq1_linear_f16 with M == 1, but the scratch (status words
+ * Same arithmetic and result as tq1_linear_f16 with M == 1, but the scratch (control words
  * and per-chunk partial-sum slots) lives in a 2 MiB array built into the library,
  * which every GPU that loads the library holds until the process exits.
  *   - Limits: K % 512 == 0, blocks 16-byte aligned, and N*K/64 + 256 bytes of scratch must
@@ -188,12 +189,78 @@ int tq1_linear_f16_sharded(const uint8_t *blocks, const void *x, const tq1_shard
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress) with that device current; make that first call outside any
  *     stream capture.
- *   - Every call on a device shares the one array and clears the part it uses on `stream` first,
- *     so calls that may overlap on the GPU (different streams) race with each other; keep
- *     them on one stream or order them with events.
- *   - Calls no cudaMalloc, cudaFree or allocating library routine. */
+ *   - Every call on a device shares the one array, which keeps what the last call left: the
+ *     partial sums carry sequence tags, so nothing has to start at zero except the array's
+ *     initial state, but calls that may overlap on the GPU (different streams) race with
+ *     each other; keep them on one stream or order them with events.
+ *   - Calls no cudaMalloc, cudaFree or allocating library routine.
+ *   - A bounded wait that ran out inside the kernel leaves a non-zero status word in the
+ *     array (and a wrong y); it stays until the process exits. tq1_gemv_noalloc_status
+ *     copies it to host memory on `stream` (4 bytes, no allocation). */
 int tq1_gemv_f16_noalloc(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
                          int N, int K, void *stream);
+int tq1_gemv_noalloc_status(uint32_t *status_host, void *stream);
+
+/* ---- a chain of batch-1 products in one launch ----------------------------- */
+
+/* A decoded token runs one matrix-vector product per packed linear, back to back: the
+ * reference's converted model calls packed_matmul for q/k/v, o, gate/up and down of every
+ * layer (src/ternel_mlx/modules.py:425-457,460-495), one kernel launch each. A chain runs a
+ * list of such products ("links") inside one persistent kernel: the next link's weights are
+ * already streaming while the current one finishes, and a link that reads an earlier link's
+ * output waits, element by element, for exactly the activations it needs. The arithmetic of
+ * every link is that of tq1_linear_f16 with M == 1 (bit-identical results).
+ *
+ * Link i computes  out = f(W_i x_i) * out_scale  with f the identity or, with swiglu != 0,
+ * silu(gate) * up over (gate, up) row pairs as in tq1_linear_swiglu_f16; `out` has N (or N/2)
+ * elements, is rounded to FP16 for any later link that reads it, and is stored to y (FP16 or
+ * FP32) when y is not NULL. */
+typedef struct tq1_chain_link {
+    const uint8_t *blocks; /* device, canonical [N][K/128][28], 16-byte aligned; this rank's rows */
+    int N, K;              /* K % 512 == 0, K <= 65536 */
+    const void *x;         /* device FP16 [K], complete before the launch; NULL: read link `source` */
+    int source;            /* with x == NULL: index of an EARLIER link whose output is this link's input */
+    int source_offset;     /* first element of that output to read (e.g. the q part of a fused q|k|v) */
+    void *y;               /* device output of this rank's rows, or NULL */
+    int y_is_f32;
+    int swiglu;            /* rows are (gate, up) pairs: N/2 outputs */
+    float out_scale;       /* multiplies every output; 0 is taken as 1 */
+} tq1_chain_link;
+
+/* Row-sharded chains: every rank runs the same list over its own rows of every matrix (rank r owns
+ * output elements [r * n_out, (r + 1) * n_out) of each link) and each finished output is written,
+ * as a 64-bit word {FP16 bits, sequence tag}, straight into the hand-off area of EVERY rank (plain
+ * peer stores over NVLink, no multicast); readers poll their own memory. handoff[r] is rank r's
+ * area (tq1_chain_handoff_bytes, zero-filled once, 256-byte aligned, mapped into this process).
+ * Every rank must issue the same sequence of chain calls on its area. The reference has no
+ * multi-device path (patches/prism-tq1-g128-distribution.patch:373). */
+typedef struct tq1_chain_peers {
+    int rank, world;       /* world <= 8 */
+    void *handoff[8];
+} tq1_chain_peers;
+
+/* Bytes of workspace a chain needs: control words, two alternating 8 MiB slot regions and, on a
+ * single GPU (world <= 1), the hand-off words of the links behind them. Zero-fill once. A chain
+ * workspace may also serve tq1_linear_f16 calls with M == 1, but not M >= 2 calls (their scratch
+ * would overwrite hand-off words). */
+size_t tq1_chain_workspace_bytes(const tq1_chain_link *links, int n_links, int world);
+size_t tq1_chain_handoff_bytes(const tq1_chain_link *links, int n_links, int world);
+
+/* Up to 8 links, described on the spot (single GPU). */
+int tq1_linear_chain_f16(const tq1_chain_link *links, int n_links, void *workspace, size_t workspace_bytes,
+                         void *stream);
+
+/* Longer chains (a whole decode step) are described once: the link table lives in caller-owned
+ * device memory (tq1_chain_table_bytes, 128-byte aligned; uploaded on `stream`), the returned
+ * handle is a small host object. tq1_chain_plan_run enqueues one launch; the plan keeps the
+ * pointers it was created with (weights, x, y, workspace, hand-off areas). */
+typedef struct tq1_chain_plan tq1_chain_plan;
+size_t tq1_chain_table_bytes(const tq1_chain_link *links, int n_links);
+int tq1_chain_plan_create(const tq1_chain_link *links, int n_links, const tq1_chain_peers *peers,
+                          void *workspace, size_t workspace_bytes, void *table, size_t table_bytes,
+                          void *stream, tq1_chain_plan **out);
+int tq1_chain_plan_run(const tq1_chain_plan *plan, void *stream);
+void tq1_chain_plan_destroy(tq1_chain_plan *plan);
 
 /* out[t][k] = (c[id_t][k]-1) * scale[id_t][k/128], exact; an id outside [0,V)
  * gives a zero row. Replaces tq1_get_rows (src/ternel_mlx/kernels.py:1360-1398,

@@ -42,6 +42,15 @@ SIGNATURES = {
     "tq1_linear_f16_sharded": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t,
                                        c_void_p]),
     "tq1_gemv_f16_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tq1_gemv_noalloc_status": (c_int, [c_void_p, c_void_p]),
+    "tq1_chain_workspace_bytes": (c_size_t, [c_void_p, c_int, c_int]),
+    "tq1_chain_handoff_bytes": (c_size_t, [c_void_p, c_int, c_int]),
+    "tq1_chain_table_bytes": (c_size_t, [c_void_p, c_int]),
+    "tq1_linear_chain_f16": (c_int, [c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
+    "tq1_chain_plan_create": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_size_t, c_void_p, c_size_t,
+                                      c_void_p, POINTER(c_void_p)]),
+    "tq1_chain_plan_run": (c_int, [c_void_p, c_void_p]),
+    "tq1_chain_plan_destroy": (None, [c_void_p]),
     "tq1_embedding_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int,
                                   c_void_p]),
 }
@@ -54,6 +63,20 @@ class Shard(ctypes.Structure):
         ("epoch_base", c_void_p), ("publish_epoch", ctypes.c_uint32), ("wait_flags", c_void_p),
         ("wait_epoch", ctypes.c_uint32), ("wait_tiles", c_int),
     ]
+
+
+class ChainLink(ctypes.Structure):
+    """Mirror of ``tq1_chain_link`` in include/ternel_b200.h."""
+    _fields_ = [
+        ("blocks", c_void_p), ("N", c_int), ("K", c_int), ("x", c_void_p), ("source", c_int),
+        ("source_offset", c_int), ("y", c_void_p), ("y_is_f32", c_int), ("swiglu", c_int),
+        ("out_scale", ctypes.c_float),
+    ]
+
+
+class ChainPeers(ctypes.Structure):
+    """Mirror of ``tq1_chain_peers`` in include/ternel_b200.h."""
+    _fields_ = [("rank", c_int), ("world", c_int), ("handoff", c_void_p * 8)]
 
 
 _lib: ctypes.CDLL | None = None

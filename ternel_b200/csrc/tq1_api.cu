@@ -10,7 +10,7 @@ extern "C" {
 
 size_t tq1_linear_workspace_bytes(int M, int N, int K) {
     if (M <= 0 || N <= 0 || K <= 0 || K % kGroup) return 0;
-    if (M == 1 && gemv_stream_shape_ok(N, K)) return gemv_stream_workspace_bytes(N, K);
+    if (M == 1 && gemv_chain_shape_ok(N, K)) return gemv_chain_workspace_bytes(N, K);
     if (gemm_tc_shape_ok(M, N, K)) return gemm_tc_workspace_bytes(M, N, K);
     return 0;
 }
@@ -31,8 +31,9 @@ int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
     if (need && (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)))
         return fail(TQ1_ERR_WORKSPACE, "tq1_linear_f16: workspace of %zu bytes (256-byte aligned) required", need);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (M == 1 && gemv_stream_supported(blocks, N, K))
-        return launch_gemv_stream(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, N, K, workspace, s);
+    if (M == 1 && gemv_chain_fits(blocks, N, K))
+        return launch_gemv_single(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, N, K, false, workspace,
+                                  kWsSlotRegionBytes, s);
     if (gemm_tc_supported(blocks, static_cast<const __half *>(x), M, N, K))
         return launch_gemm_tc(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, workspace, s);
     return launch_gemv_rows(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, s);
@@ -48,7 +49,7 @@ int tq1_linear_swiglu_f16(const uint8_t *blocks, const void *x, void *y, int y_i
     if (reinterpret_cast<uintptr_t>(x) & 15)
         return fail(TQ1_ERR_INVALID, "tq1_linear_swiglu_f16: x must be 16-byte aligned");
     const __half *xh = static_cast<const __half *>(x);
-    const bool gemv = M == 1 && gemv_stream_supported(blocks, rows, K);
+    const bool gemv = M == 1 && gemv_chain_fits(blocks, rows, K);
     if (!gemv && !gemm_tc_supported(blocks, xh, M, rows, K))
         return fail(TQ1_ERR_INVALID,
                     "tq1_linear_swiglu_f16: needs K %% 512 == 0 and 16-byte aligned blocks (got %dx%d)", rows, K);
@@ -56,11 +57,7 @@ int tq1_linear_swiglu_f16(const uint8_t *blocks, const void *x, void *y, int y_i
     if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
         return fail(TQ1_ERR_WORKSPACE, "tq1_linear_swiglu_f16: workspace of %zu bytes (256-byte aligned) required", need);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (gemv) {
-        ShardDev opt = {};
-        opt.swiglu = 1;
-        return launch_gemv_stream(blocks, xh, y, y_is_f32 != 0, rows, K, workspace, s, &opt);
-    }
+    if (gemv) return launch_gemv_single(blocks, xh, y, y_is_f32 != 0, rows, K, true, workspace, kWsSlotRegionBytes, s);
     return launch_gemm_tc(blocks, xh, y, y_is_f32 != 0, M, rows, K, workspace, s, true);
 }
 
@@ -68,7 +65,7 @@ int tq1_linear_plan(int M, int N, int K, int aligned, int *kernel, int *token_ti
     if (!kernel || !token_tile || !ctas || !parts) return fail(TQ1_ERR_INVALID, "tq1_linear_plan: null pointer");
     if (M <= 0 || N <= 0 || K <= 0 || K % kGroup) return fail(TQ1_ERR_INVALID, "tq1_linear_plan: bad shape");
     *token_tile = *ctas = *parts = 0;
-    if (M == 1 && aligned && gemv_stream_shape_ok(N, K)) {
+    if (M == 1 && aligned && gemv_chain_shape_ok(N, K)) {
         *kernel = TQ1_KERNEL_STREAM_GEMV;
     } else if (aligned && gemm_tc_shape_ok(M, N, K)) {
         *kernel = TQ1_KERNEL_TENSOR_CORE;
@@ -138,9 +135,7 @@ int tq1_linear_f16_sharded(const uint8_t *blocks, const void *x, const tq1_shard
     sd.ld_total = shard->n_total;
     unsigned *status = static_cast<unsigned *>(workspace);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (M == 1 && gemv_stream_supported(blocks, N_local, K))     // the GEMV's epilogue does the push itself
-        return launch_gemv_stream(blocks, static_cast<const __half *>(x), nullptr, false, N_local, K, workspace, s, &sd);
-    // general path: wait for the inputs, compute the local slice, push it
+    // wait for the inputs, compute the local slice, push it
     int rc = launch_shard_wait(sd, status, s);
     if (rc != TQ1_OK) return rc;
     const size_t base = need - shard_local_bytes(M, N_local);
@@ -160,6 +155,11 @@ int tq1_gemv_f16_noalloc(const uint8_t *blocks, const void *x, void *y, int y_is
         return fail(TQ1_ERR_INVALID, "tq1_gemv_f16_noalloc: x must be 16-byte aligned");
     return gemv_noalloc(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, N, K,
                         static_cast<cudaStream_t>(stream));
+}
+
+int tq1_gemv_noalloc_status(uint32_t *status_host, void *stream) {
+    if (!status_host) return fail(TQ1_ERR_INVALID, "tq1_gemv_noalloc_status: null pointer");
+    return gemv_noalloc_status(status_host, static_cast<cudaStream_t>(stream));
 }
 
 int tq1_embedding_f16(const uint8_t *blocks, const int64_t *ids, void *out, int out_is_f32,

@@ -16,10 +16,11 @@ constexpr int kFullBytes = 25;
 constexpr int kMaxFull = 242;
 constexpr int kMaxTail = 26;
 
-// Workspace layout shared by every linear kernel: [status words, 256 B][partial-sum slots of the
-// batch-1 kernel, 16 MiB][scratch of the batched kernel]. The slot region must be zero between
-// calls (its users leave it so) and no other kernel writes there, so calls of any shape and kind
-// can share one workspace. A batch-1 shape whose slots need more than the region takes the batched path.
+// Workspace layout shared by every linear kernel: [control words, 256 B][partial-sum slots of the
+// batch-1 kernel, 16 MiB][scratch of the batched kernel, or the hand-off words of a chain]. Slots
+// carry sequence tags, so nothing in the slot region ever has to be cleared; no other kernel writes
+// there, so calls of any shape and kind can share one workspace. The workspace must be zero-filled
+// once before its first use.
 constexpr size_t kWsStatusBytes = 256;
 constexpr size_t kWsSlotRegionBytes = (size_t)16 << 20;
 constexpr size_t kWsScratchOffset = kWsStatusBytes + kWsSlotRegionBytes;
@@ -55,17 +56,21 @@ struct ShardDev {
     int swiglu;                         // unsharded only: rows are (gate, up) pairs, y[i] = silu(gate_i) * up_i
 };
 
-// Streaming batch-1 GEMV (TMA + integer tensor cores); needs K % 512 == 0 and 16-byte aligned blocks.
-bool gemv_stream_shape_ok(int N, int K);
-bool gemv_stream_supported(const uint8_t *blocks, int N, int K);
-size_t gemv_stream_workspace_bytes(int N, int K);
-int launch_gemv_stream(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K,
-                       void *workspace, cudaStream_t stream, const ShardDev *shard = nullptr);
+// Batch-1 GEMV as a persistent chain of links (TMA + integer tensor cores); needs K % 512 == 0, at most
+// 128 K chunks and 16-byte aligned blocks. A single product is a chain of one link.
+bool gemv_chain_shape_ok(int N, int K);
+bool gemv_chain_supported(const uint8_t *blocks, int N, int K);
+bool gemv_chain_fits(const uint8_t *blocks, int N, int K);      // also checks the current device's SM count
+size_t gemv_chain_workspace_bytes(int N, int K);
+// slot_bytes: room for partial-sum slots behind the workspace's control words
+int launch_gemv_single(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K, bool swiglu,
+                       void *workspace, size_t slot_bytes, cudaStream_t stream);
 int launch_shard_wait(const ShardDev &shard, unsigned *status, cudaStream_t stream);
 int launch_shard_push(const __half *local, int M, int n_local, const ShardDev &shard, cudaStream_t stream);
 int launch_epoch_advance(unsigned *epoch_base, unsigned delta, cudaStream_t stream);
 
 int gemv_noalloc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K, cudaStream_t stream);
+int gemv_noalloc_status(unsigned *out_host, cudaStream_t stream);
 
 // Batched linear (M >= 2) on tcgen05 tensor cores; needs K % 512 == 0 and 16-byte aligned pointers.
 bool gemm_tc_shape_ok(int M, int N, int K);

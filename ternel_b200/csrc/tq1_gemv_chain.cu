@@ -1,0 +1,1196 @@
+// Batch-1 GEMV for TQ1_G128 on sm_100a as ONE persistent launch over a chain of projections.
+//
+// A decoded token issues one matrix-vector product per packed linear, back to back
+// (src/ternel_mlx/modules.py:425-457 of the reference: q/k/v, o, gate/up, down, layer after
+// layer). Launched one by one, each product pays a launch hand-over, a cold pipeline and a
+// reduction tail that together cost as much as streaming its weights. Here a whole list of
+// products ("links") runs inside one grid of persistent CTAs:
+//
+//   * the weight tiles of the next link are already being fetched (TMA into each warp's
+//     ring) while the current one drains;
+//   * a link that reads the output of an earlier link waits for exactly the activations it
+//     needs, element by element: an output travels as one 64-bit word {value bits, tag}
+//     written by a single store, so whoever sees the tag has the value (no fence, no flag
+//     array, no second round trip). The same words are pushed into every rank's memory when
+//     the rows of a projection are sharded over several GPUs (plain peer stores);
+//   * the table, the barriers and the CTA's bookkeeping are set up once.
+//
+// The arithmetic is the exact-integer scheme of the streaming GEMV: a code byte b becomes,
+// through a lane-replicated 243-entry shared-memory table, four signed weights w0..w3 that
+// are used directly as an A register of mma.sync.m16n8k32.s8; the fifth trit is never
+// extracted because b = sum_i 3^i (w_i + 1) gives
+//     81 * sum_{i<5} w_i x_i = sum_{i<4} w_i (81 x_i - 3^i x_4) + (b - 121) x_4 ,
+// so the raw code words serve as unsigned A registers against x_4. Activations are block
+// fixed point (23 bits below the group's maximum, as exact as FP32 accumulation) split into
+// four signed byte planes; s32 accumulators give 81 * (group sum) modulo 2^32, a multiplication
+// by 81^-1 (mod 2^32) recovers the integer, then acc = fma(scale_g, 2^(E-21) * sum, acc) in
+// FP32 as in src/bonsai_tq1/reference.py:33-38. Groups holding NaN/Inf activations take an
+// FP32 path that multiplies every weight, so non-finite values propagate as in the reference.
+//
+// Work decomposition per link: a unit is 16 rows x 4 groups (1792 bytes, one TMA box); units
+// are numbered chunk-major (a chunk = 512 columns) and dealt out in contiguous ranges to the
+// warps of the persistent CTAs, so a warp keeps the activation digits of one chunk in
+// registers while it streams row tiles. A warp's chunk partial of a row goes to a 64-bit
+// workspace slot {FP32 value, tag}; row tile t has a fixed owner (the warp that processed
+// chunk t % chunks of it), which polls the tile's slots (bounded), adds the chunks in
+// ascending order (results never depend on timing) and stores the output. Tags are
+// sequence numbers that grow with every link of every call, so nothing has to be cleared.
+// Two slot regions alternate between consecutive links; a per-region arrival counter keeps
+// a CTA that runs ahead from overwriting slots that have not been summed yet.
+//
+// Shared-memory traffic sets the pace of the loop (one 128-byte wavefront per 32 code bytes
+// for the table alone), so the loop spends as few load/store-pipe operations as it can:
+// plane pairs are combined before they are exchanged (two shuffles per 16 rows x 2 groups
+// instead of four), slots are never cleared, and the digit planes are written without bank
+// conflicts.
+#include <cuda.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <vector>
+
+#include "tq1_common.cuh"
+
+namespace tq1 {
+
+namespace {
+
+constexpr int kTileRows = 16;
+constexpr int kChunkGroups = 4;
+constexpr int kChunkCols = kChunkGroups * kGroup;             // 512
+constexpr int kChunkBytes = kChunkGroups * kBlockBytes;       // 112
+constexpr int kUnitBytes = kTileRows * kChunkBytes;           // 1792
+constexpr int kStages = 4;
+constexpr int kWarps = 16;
+constexpr int kThreads = kWarps * 32;
+constexpr int kMaxChunksPerCta = 3;
+constexpr int kRegsPerSub = 18;                                // A/B registers per lane per sub-unit
+static_assert((kStages & (kStages - 1)) == 0, "stage index is taken with a mask");
+
+// Shared-memory window layout (addresses relative to the CTA's shared window). The table sits
+// at a 64 KiB multiple so that PRMT can build a complete lookup address
+// (byte << 8 | lane << 2 | table base) in one instruction. It holds 256 entries (the 13 past
+// 242 are zero), so a byte that escaped the load-time scan still reads inside the table.
+constexpr uint32_t kLutWindowAddr = 131072;
+constexpr uint32_t kLutBytes = 256 * 256;                     // 256 entries x (2 x 32 lanes x 4 B)
+constexpr uint32_t kWindowEnd = kLutWindowAddr + kLutBytes;   // 196608
+constexpr uint32_t kRingBytes = kWarps * kStages * kUnitBytes;                     // 114688
+constexpr uint32_t kBtabOne = kMaxChunksPerCta * 2 * kRegsPerSub * 32 * 4;         // 13824 per buffer
+constexpr uint32_t kBtabBytes = 2 * kBtabOne;                                      // two links in flight
+constexpr uint32_t kMbarBytes = 8 * (kWarps * kStages + 2);
+constexpr uint32_t kRedOne = 3 * 4 * kWarps * kMaxChunksPerCta;                    // group max / sum / non-finite
+constexpr uint32_t kRedBytes = 2 * kRedOne;
+constexpr uint32_t kHighBytes = kBtabBytes + kMbarBytes + kRedBytes;
+static_assert(kRingBytes + 1024 + 128 <= kLutWindowAddr, "the ring must end below the table's fixed address");
+static_assert(kWindowEnd + kHighBytes <= 227 * 1024, "shared memory budget");
+constexpr uint32_t kMaxWaitSpins = 1u << 21;
+
+// Control words at the start of the workspace.
+constexpr int kCtlStatus = 0;      // non-zero: a bounded wait ran out (1 tile, 4 hand-off word, 5 slot, 6 region)
+constexpr int kCtlExit = 1;        // CTAs that have left the current launch
+constexpr int kCtlEpoch = 2;       // links executed by all earlier launches on this workspace (tag base)
+constexpr int kCtlArrive = 3;      // [2] CTAs that are done with the slots of the links of each region
+
+constexpr unsigned kFlagOutF32 = 1u;
+constexpr unsigned kFlagSwiglu = 2u;
+
+// One link as the kernel sees it.
+struct alignas(128) ChainLinkDev {
+    CUtensorMap wmap;                           // [rows][row bytes] of this link's canonical blocks
+    const __half *x;                            // FP16 activations written before the launch, or null
+    const unsigned long long *xin;              // hand-off words of the producing link (first element read), or null
+    void *y;                                    // FP16/FP32 output, or null
+    unsigned long long *xout[kMaxRanks];        // per rank: hand-off words of this link's output, at this rank's first
+                                                // output element (null: nobody reads this link inside the chain)
+    int N, K, tiles, chunks;
+    int src_tag;                                // tag offset of the producing link
+    int tag;                                    // tag offset of this link
+    int world;                                  // ranks the output is pushed to
+    unsigned flags;
+    float out_scale;
+    int pad[1];
+};
+static_assert(sizeof(ChainLinkDev) == 256, "link descriptor size");
+
+constexpr int kInlineLinks = 8;
+struct ChainParams {
+    const ChainLinkDev *table;                  // device table, or null: the links are inl[]
+    unsigned *ctl;
+    unsigned long long *slots;
+    unsigned long long region_slots;            // slots per region
+    int n_links;
+    int n_regions;                              // 1 (single link only) or 2
+    unsigned tag_advance;                       // how far this launch moves the tag base
+    int pad;
+    ChainLinkDev inl[kInlineLinks];
+};
+
+struct LutImage {
+    uint32_t w[256 * 64];
+};
+constexpr LutImage make_lut_image() {
+    LutImage img{};
+    for (int v = 0; v < 243; ++v) {
+        uint32_t entry = 0;
+        int t = v;
+        for (int d = 0; d < 4; ++d) {
+            entry |= (uint32_t)((t % 3 - 1) & 0xff) << (8 * d);
+            t /= 3;
+        }
+        for (int l = 0; l < 32; ++l) img.w[v * 64 + l] = entry;
+    }
+    return img;
+}
+__device__ __align__(128) const LutImage g_chain_lut = make_lut_image();
+static_assert(sizeof(LutImage) == kLutBytes, "table image size");
+
+template <uint32_t SEL>
+__device__ __forceinline__ uint32_t prmt_imm(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "n"(SEL));
+    return d;
+}
+// Ring-buffer words. Not volatile: the address depends on the value returned by the barrier wait,
+// which keeps the loads behind it while leaving the compiler free to interleave the two sub-units.
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_off(uint32_t addr) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_lut(uint32_t addr) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+template <bool SIGNED_A, bool ZERO_C>
+__device__ __forceinline__ void mma_bytes(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    if (ZERO_C) {
+        if (SIGNED_A)
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+        else
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+    } else {
+        if (SIGNED_A)
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+        else
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// One lane-stream (half a block: 14 code-byte slots in four words, wa holding slots 0,1 in its
+// upper half) becomes 18 A registers: 14 table entries (weights of trits 0..3 of each slot) and
+// the four raw words (the code bytes themselves, paired with the fifth trit's activation).
+__device__ __forceinline__ void decode_stream(uint32_t wa, uint32_t wb, uint32_t wc, uint32_t wd,
+                                              uint32_t lane_base, uint32_t (&r)[kRegsPerSub]) {
+    r[0] = lds_lut(prmt_imm<0x7624>(wa, lane_base));
+    r[1] = lds_lut(prmt_imm<0x7634>(wa, lane_base));
+    r[2] = lds_lut(prmt_imm<0x7604>(wb, lane_base));
+    r[3] = lds_lut(prmt_imm<0x7614>(wb, lane_base));
+    r[4] = lds_lut(prmt_imm<0x7624>(wb, lane_base));
+    r[5] = lds_lut(prmt_imm<0x7634>(wb, lane_base));
+    r[6] = lds_lut(prmt_imm<0x7604>(wc, lane_base));
+    r[7] = lds_lut(prmt_imm<0x7614>(wc, lane_base));
+    r[8] = lds_lut(prmt_imm<0x7624>(wc, lane_base));
+    r[9] = lds_lut(prmt_imm<0x7634>(wc, lane_base));
+    r[10] = lds_lut(prmt_imm<0x7604>(wd, lane_base));
+    r[11] = lds_lut(prmt_imm<0x7614>(wd, lane_base));
+    r[12] = lds_lut(prmt_imm<0x7624>(wd, lane_base));
+    r[13] = lds_lut(prmt_imm<0x7634>(wd, lane_base));
+    r[14] = wa;
+    r[15] = wb;
+    r[16] = wc;
+    r[17] = wd;
+}
+
+// 64-bit words {payload, tag}: a 64-bit store is a single access, so a reader that finds the tag
+// also has the payload.
+__device__ __forceinline__ void word_publish(unsigned long long *p, uint32_t payload, uint32_t tag) {
+    const unsigned long long w = ((unsigned long long)tag << 32) | payload;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ void slot_publish(unsigned long long *p, float v, uint32_t tag) {
+    const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long slot_read(const unsigned long long *p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+// Hand-off words may have been written by another GPU into this GPU's memory.
+__device__ __forceinline__ unsigned long long word_read(const unsigned long long *p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+__device__ __forceinline__ unsigned ctl_read(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Activation `idx` of a link, whichever form it arrives in (the hand-off word has been waited for).
+__device__ __forceinline__ float link_x(const __half *x, const unsigned long long *xin, size_t idx) {
+    if (x) return __half2float(x[idx]);
+    return __half2float(__ushort_as_half((unsigned short)(word_read(xin + idx) & 0xffffu)));
+}
+
+// FP32 fallback for one block (row-major canonical bytes in shared memory): multiplies every
+// weight so that NaN and Inf propagate exactly as in the reference.
+__device__ float block_dot_fp32(const uint8_t *blk, const __half *x, const unsigned long long *xin, size_t x0) {
+    float sum = 0.0f;
+    for (int j = 0; j < kCodeBytes; ++j) {
+        uint32_t v = blk[2 + j];
+        const int n = j == 25 ? 3 : 5;
+        for (int i = 0; i < n; ++i) {
+            const float w = (float)((int)(v % 3u) - 1);
+            v /= 3u;
+            sum = fmaf(w, link_x(x, xin, x0 + 5 * j + i), sum);
+        }
+    }
+    return sum;
+}
+
+// Units of a link that one warp of one CTA processes (units are numbered chunk-major).
+struct WarpRange {
+    int n_units, c_first, t_first;
+    int chunk_lo, chunk_hi;                 // chunks the CTA touches (chunk_hi < chunk_lo: none)
+};
+__device__ __forceinline__ WarpRange warp_range(int tiles, int chunks, int warp) {
+    WarpRange r;
+    // tiles * chunks <= 2^22 and gridDim.x <= a few hundred, so the products fit 32 bits
+    const unsigned total = (unsigned)tiles * (unsigned)chunks;
+    const int cta_begin = (int)(total * blockIdx.x / gridDim.x);
+    const int cta_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
+    const int cta_units = cta_end - cta_begin;
+    const int u_begin = cta_begin + ((cta_units * warp) >> 4);
+    const int u_end = cta_begin + ((cta_units * (warp + 1)) >> 4);
+    r.n_units = u_end - u_begin;
+    r.chunk_lo = cta_units > 0 ? cta_begin / tiles : 0;
+    r.chunk_hi = cta_units > 0 ? (cta_end - 1) / tiles : -1;
+    r.c_first = u_begin / tiles;
+    r.t_first = u_begin - r.c_first * tiles;
+    return r;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __grid_constant__ ChainParams P) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const uint32_t window = (uint32_t)__cvta_generic_to_shared(smem);
+    unsigned char *ring = smem;
+    unsigned char *high = smem + (kWindowEnd - window);
+    uint32_t *btab_all = reinterpret_cast<uint32_t *>(high);
+    uint64_t *mbars = reinterpret_cast<uint64_t *>(high + kBtabBytes);
+    unsigned char *red_all = high + kBtabBytes + kMbarBytes;
+    unsigned *ctl = P.ctl;
+    if (window + kRingBytes > kLutWindowAddr) {      // the fixed-address table would overlap the ring
+        if (threadIdx.x == 0) atomicExch(ctl + kCtlStatus, 2u);
+        return;
+    }
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int n_links = P.n_links;
+    const ChainLinkDev *links = P.table ? P.table : P.inl;
+
+    // ---- barriers, decode table, empty digit planes: nothing here depends on earlier kernels --------
+    const uint32_t ring_warp = window + (uint32_t)(warp * kStages * kUnitBytes);
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&mbars[warp * kStages]);
+    const uint32_t lut_bar = (uint32_t)__cvta_generic_to_shared(&mbars[kWarps * kStages]);
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8u * s, 1);
+        if (warp == 0) mbar_init(lut_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (warp == 0) {
+            mbar_expect_tx(lut_bar, kLutBytes);
+            bulk_load(kLutWindowAddr, &g_chain_lut, kLutBytes, lut_bar);
+        }
+    }
+    // k-slots of the other group of a sub-unit stay zero for the whole launch; the live bytes are
+    // rewritten for every link
+    for (int i = tid; i < (int)(kBtabBytes / 16); i += kThreads)
+        reinterpret_cast<uint4 *>(btab_all)[i] = make_uint4(0u, 0u, 0u, 0u);
+
+    // ---- producer cursor: the next unit this warp requests, possibly of a later link ------------------
+    int issued = 0, consumed = 0;               // units requested / finished by this warp since the launch began
+    int iss_link = 0, iss_left, iss_c, iss_t, iss_tiles;
+    const CUtensorMap *iss_map;
+    auto cursor_load = [&]() {
+        const ChainLinkDev &L = links[iss_link];
+        const WarpRange r = warp_range(L.tiles, L.chunks, warp);
+        iss_left = r.n_units; iss_c = r.c_first; iss_t = r.t_first; iss_tiles = L.tiles;
+        iss_map = &L.wmap;
+    };
+    cursor_load();
+    auto issue_one = [&]() -> bool {            // lane 0 only; false when the chain has no unit left for this warp
+        while (iss_left == 0) {
+            if (iss_link + 1 >= n_links) return false;
+            ++iss_link;
+            cursor_load();
+        }
+        const uint32_t s = (uint32_t)issued & (kStages - 1);
+        mbar_expect_tx(bar0 + 8u * s, kUnitBytes);
+        tma_load_2d(ring_warp + s * kUnitBytes, iss_map, iss_c * kChunkBytes, iss_t * kTileRows, bar0 + 8u * s);
+        ++issued;
+        --iss_left;
+        if (++iss_t == iss_tiles) { iss_t = 0; ++iss_c; }
+        return true;
+    };
+    if (tid == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(iss_map) : "memory");
+
+    // Let the next kernel in the stream start its own prologue as SMs free up, then wait until
+    // everything before this kernel has finished before touching activations or the workspace.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const unsigned tag_base = ctl_read(ctl + kCtlEpoch);
+
+    const int g = lane >> 2, q = lane & 3;
+    const int cls = q >> 1, h = q & 1;
+    const uint32_t lane_base = kLutWindowAddr + (uint32_t)lane * 4u;
+    // byte offset of this lane's first half-block inside a tile (sub-unit 0, row g)
+    const uint32_t lane_tile_off = (uint32_t)(((g * kChunkGroups + 2 * cls) * kBlockWords + 3 * h) * 4);
+
+    // activation roles of the prologue: one thread per activation of a chunk
+    const int gi = tid >> 7;                           // group within the chunk
+    const int el = tid & 127;
+    const int bj = el < 125 ? el / 5 : 25;             // code byte
+    const int bi = el < 125 ? el - 5 * bj : el - 125;  // trit within the byte
+    const bool is_fifth = el < 125 && bi == 4;         // pairs with the raw code byte
+    const int fifth = el < 125 ? gi * kGroup + 5 * bj + 4 : tid;
+    uint32_t plane_off;                                // byte offset of this activation's digit 0 inside a chunk's planes
+    {
+        const int hh = bj < 14 ? 0 : 1;                    // which half-block lane decodes it
+        const int slot = hh ? bj - 12 : bj;
+        // trits 0..3 sit in the table-entry register of their slot; a fifth trit pairs with the raw word
+        const int reg = !is_fifth ? slot : slot < 2 ? 14 : 15 + ((slot - 2) >> 2);
+        const int pos = !is_fifth ? bi : slot < 2 ? slot + 2 : ((slot - 2) & 3);
+        const int sub = gi & 1, cg = gi >> 1;
+        const int owner = 4 * (4 * cg) + 2 * cg + hh;      // B lane of digit plane 0; plane p is 4p lanes on
+        plane_off = (uint32_t)((((sub * kRegsPerSub + reg) * 32 + owner) * 4) + pos);
+    }
+    const int pow3 = bi == 0 ? 1 : bi == 1 ? 3 : bi == 2 ? 9 : 27;
+
+    bool dead = false;                                 // a bounded wait ran out: stop waiting, finish quickly
+    __syncthreads();                                   // barriers initialised, planes zeroed
+
+    for (int p = 0; p < n_links; ++p) {
+        const ChainLinkDev &L = links[p];
+        const int N = L.N, tiles = L.tiles, chunks = L.chunks;
+        const __half *xh = L.x;
+        const unsigned long long *xin = L.xin;
+        const unsigned flags = L.flags;
+        const WarpRange R = warp_range(tiles, chunks, warp);
+        const int n_units = R.n_units, chunk_lo = R.chunk_lo, chunk_hi = R.chunk_hi;
+        const int buf = p & 1;
+        uint32_t *btab = btab_all + buf * (kBtabOne / 4);
+        float *red_max = reinterpret_cast<float *>(red_all + buf * kRedOne);       // [chunk][warp]
+        int *red_sum = reinterpret_cast<int *>(red_max + kMaxChunksPerCta * kWarps);
+        int *red_bad = red_sum + kMaxChunksPerCta * kWarps;
+        const unsigned tag = tag_base + (unsigned)L.tag + 1u;
+
+        // ---- this CTA's activations: one thread per activation, which also fetches the activation
+        // of the fifth trit of its code byte (needed for 81 x_i - 3^i x_4) -----------------------------
+        float xv[kMaxChunksPerCta], x4v[kMaxChunksPerCta];
+        if (xin == nullptr) {
+#pragma unroll
+            for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
+                const bool live = chunk_lo + cl <= chunk_hi;
+                const __half *xc = xh + (size_t)(chunk_lo + cl) * kChunkCols;
+                xv[cl] = live ? __half2float(xc[tid]) : 0.0f;
+                x4v[cl] = live ? __half2float(xc[fifth]) : 0.0f;
+            }
+            // The activation loads are in flight: now start this warp's weight tiles (issued the other
+            // way round the few activation bytes queue behind megabytes of weight traffic). One tile
+            // per warp for now, so that every warp's first tile is near the head of the queue.
+            if (lane == 0 && issued == consumed) issue_one();
+        } else {
+            // Output of an earlier link: keep the weight pipeline full, then wait (bounded) for exactly the
+            // words this thread needs.
+            if (lane == 0)
+                while (issued - consumed < kStages - 1 && issue_one()) {}
+            const unsigned want = tag_base + (unsigned)L.src_tag + 1u;
+            unsigned long long wv[kMaxChunksPerCta], w4[kMaxChunksPerCta];
+#pragma unroll
+            for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
+                const bool live = chunk_lo + cl <= chunk_hi;
+                const unsigned long long *xc = xin + (size_t)(chunk_lo + cl) * kChunkCols;
+                wv[cl] = live ? word_read(xc + tid) : ((unsigned long long)want << 32);
+                w4[cl] = live ? word_read(xc + fifth) : ((unsigned long long)want << 32);
+            }
+#pragma unroll
+            for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
+                const unsigned long long *xc = xin + (size_t)(chunk_lo + cl) * kChunkCols;
+                uint32_t spins = 0;
+                while ((unsigned)(wv[cl] >> 32) != want && !dead) {
+                    if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 4u); dead = true; break; }
+                    wv[cl] = word_read(xc + tid);
+                }
+                while ((unsigned)(w4[cl] >> 32) != want && !dead) {
+                    if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 4u); dead = true; break; }
+                    w4[cl] = word_read(xc + fifth);
+                }
+                xv[cl] = __half2float(__ushort_as_half((unsigned short)(wv[cl] & 0xffffu)));
+                x4v[cl] = __half2float(__ushort_as_half((unsigned short)(w4[cl] & 0xffffu)));
+            }
+        }
+
+        // ---- activation digits: group maximum, fixed point, four signed byte planes --------------------
+        bool bad[kMaxChunksPerCta];
+        const int n_chunks_cta = chunk_hi - chunk_lo + 1;
+#pragma unroll
+        for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
+            if (cl >= n_chunks_cta) break;
+            const float a = fabsf(xv[cl]);
+            bad[cl] = !(a <= 65504.0f);                        // NaN or Inf
+            float m = bad[cl] ? 0.0f : a;
+            int anybad = bad[cl];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                anybad |= __shfl_xor_sync(0xffffffffu, anybad, o);
+            }
+            if (lane == 0) { red_max[cl * kWarps + warp] = m; red_bad[cl * kWarps + warp] = anybad; }
+        }
+        __syncthreads();
+        // Every warp of this CTA has left link p-1, so the CTA is done with that link's slots; and
+        // before anybody publishes into the region link p shares with link p-2, every CTA must be
+        // done with link p-2's slots.
+        if (tid == 0) {
+            if (p >= 1) atomicAdd(ctl + kCtlArrive + ((p - 1) & 1), 1u);
+            if (p >= 2 && P.n_regions > 1) {
+                const unsigned need = gridDim.x * (unsigned)(p >> 1);
+                uint32_t spins = 0;
+                while (ctl_read(ctl + kCtlArrive + (p & 1)) < need) {
+                    if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 6u); break; }
+                }
+            }
+        }
+        // every warp's first tile is on its way: now queue the rest of the ring behind them
+        if (lane == 0)
+            while (issued - consumed < kStages - 1 && issue_one()) {}
+        {
+            const int gw = warp & ~3;                          // the four warps of this thread's group
+#pragma unroll
+            for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
+                if (cl >= n_chunks_cta) break;
+                const float *rm = red_max + cl * kWarps + gw;
+                const float m = fmaxf(fmaxf(rm[0], rm[1]), fmaxf(rm[2], rm[3]));
+                // 2^E <= m < 2^(E+1); fixed point xi = round(v * 2^(21-E)), |xi| <= 2^22
+                const int e_biased = m > 0.0f ? (int)(__float_as_uint(m) >> 23) : 127;
+                const float up = __uint_as_float((uint32_t)(275 - e_biased) << 23);            // 2^(21-E)
+                const int xi = bad[cl] ? 0 : __float2int_rn(xv[cl] * up);
+                int s = is_fifth ? 121 * xi : 0;                   // 121 * sum of the fifth-trit activations
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (lane == 0) red_sum[cl * kWarps + warp] = s;
+                // value paired with this k-slot: x_4 for the raw byte, 81 x_i - 3^i x_4 for trit i < 4
+                int v = xi;
+                if (!is_fifth) {
+                    const float a4 = fabsf(x4v[cl]);
+                    const int x4 = (el < 125 && a4 <= 65504.0f) ? __float2int_rn(x4v[cl] * up) : 0;
+                    v = 81 * xi - pow3 * x4;
+                }
+                const int d0 = (v << 24) >> 24;
+                const int r1 = (v - d0) >> 8;
+                const int d1 = (r1 << 24) >> 24;
+                const int r2 = (r1 - d1) >> 8;
+                const int d2 = (r2 << 24) >> 24;
+                const int d3 = (r2 - d2) >> 8;
+                unsigned char *base = reinterpret_cast<unsigned char *>(btab) + cl * (2 * kRegsPerSub * 32 * 4) + plane_off;
+                base[0] = (unsigned char)d0;
+                base[16] = (unsigned char)d1;
+                base[32] = (unsigned char)d2;
+                base[48] = (unsigned char)d3;
+            }
+        }
+        __syncthreads();
+
+        if (p == 0) {                                   // the decode table must have landed
+            uint32_t spins = 0;
+            while (!mbar_try_wait(lut_bar, 0)) {
+                if (++spins > kMaxWaitSpins) { if (lane == 0) atomicExch(ctl + kCtlStatus, 1u); dead = true; break; }
+            }
+        }
+
+        // ---- per-warp streaming loop -------------------------------------------------------------------
+        unsigned long long *slots = P.slots + (P.n_regions > 1 ? (size_t)(p & 1) * P.region_slots : 0);
+        uint32_t breg[2][kRegsPerSub];
+        int gsum[2];
+        float gpow[2];
+        int gbad[2];
+        int cur_chunk = -1;
+        int c = R.c_first, t = R.t_first;
+
+        for (int i = 0; i < n_units; ++i) {
+            if (c != cur_chunk) {       // (re)load the B fragments and the group constants of this K chunk
+                cur_chunk = c;
+                const int cl = c - chunk_lo;
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub) {
+#pragma unroll
+                    for (int r = 0; r < kRegsPerSub; ++r)
+                        breg[sub][r] = btab[((cl * 2 + sub) * kRegsPerSub + r) * 32 + lane];
+                    const int w4 = cl * kWarps + 4 * (sub + 2 * cls);          // the group's four warps
+                    gsum[sub] = red_sum[w4] + red_sum[w4 + 1] + red_sum[w4 + 2] + red_sum[w4 + 3];
+                    const float gm = fmaxf(fmaxf(red_max[w4], red_max[w4 + 1]), fmaxf(red_max[w4 + 2], red_max[w4 + 3]));
+                    const int eb = gm > 0.0f ? (int)(__float_as_uint(gm) >> 23) : 127;
+                    gpow[sub] = __uint_as_float((uint32_t)(eb - 21) << 23);                    // 2^(E-21)
+                    gbad[sub] = red_bad[w4] | red_bad[w4 + 1] | red_bad[w4 + 2] | red_bad[w4 + 3];
+                }
+            }
+            const uint32_t s = (uint32_t)consumed & (kStages - 1);
+            const uint32_t parity = ((uint32_t)consumed / kStages) & 1u;
+            uint32_t arrived = 0;
+            if (!dead) {
+                uint32_t spins = 0;
+                while (!(arrived = mbar_try_wait(bar0 + 8u * s, parity))) {
+                    if (++spins > kMaxWaitSpins) {          // never hang: flag the failure and stop waiting
+                        if (lane == 0) atomicExch(ctl + kCtlStatus, 1u);
+                        dead = true;
+                        break;
+                    }
+                }
+            }
+            // (arrived >> 8) is zero, but only the hardware knows: the tile loads depend on the wait
+            const uint32_t tile_addr = ring_warp + s * kUnitBytes + (arrived >> 8);
+            const uint32_t a1 = tile_addr + lane_tile_off;
+            float acc1 = 0.0f, acc2 = 0.0f;             // rows g and g+8, this lane's two groups
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub) {
+                constexpr int kRow8 = 8 * kChunkBytes;
+                const uint32_t w1a = sub ? lds_off<28>(a1) : lds_off<0>(a1);
+                const uint32_t w1b = sub ? lds_off<32>(a1) : lds_off<4>(a1);
+                const uint32_t w1c = sub ? lds_off<36>(a1) : lds_off<8>(a1);
+                const uint32_t w1d = sub ? lds_off<40>(a1) : lds_off<12>(a1);
+                const uint32_t w2a = sub ? lds_off<kRow8 + 28>(a1) : lds_off<kRow8 + 0>(a1);
+                const uint32_t w2b = sub ? lds_off<kRow8 + 32>(a1) : lds_off<kRow8 + 4>(a1);
+                const uint32_t w2c = sub ? lds_off<kRow8 + 36>(a1) : lds_off<kRow8 + 8>(a1);
+                const uint32_t w2d = sub ? lds_off<kRow8 + 40>(a1) : lds_off<kRow8 + 12>(a1);
+                uint32_t r1[kRegsPerSub], r2[kRegsPerSub];
+                decode_stream(w1a, w1b, w1c, w1d, lane_base, r1);
+                decode_stream(w2a, w2b, w2c, w2d, lane_base, r2);
+                // two independent accumulator chains; register pairs 0..6 hold signed weights,
+                // pairs 7,8 the raw (unsigned) code bytes
+                int accA[4], accB[4];
+                mma_bytes<true, true>(accA, r1[0], r2[0], r1[1], r2[1], breg[sub][0], breg[sub][1]);
+                mma_bytes<true, true>(accB, r1[2], r2[2], r1[3], r2[3], breg[sub][2], breg[sub][3]);
+                mma_bytes<true, false>(accA, r1[4], r2[4], r1[5], r2[5], breg[sub][4], breg[sub][5]);
+                mma_bytes<true, false>(accB, r1[6], r2[6], r1[7], r2[7], breg[sub][6], breg[sub][7]);
+                mma_bytes<true, false>(accA, r1[8], r2[8], r1[9], r2[9], breg[sub][8], breg[sub][9]);
+                mma_bytes<true, false>(accB, r1[10], r2[10], r1[11], r2[11], breg[sub][10], breg[sub][11]);
+                mma_bytes<true, false>(accA, r1[12], r2[12], r1[13], r2[13], breg[sub][12], breg[sub][13]);
+                mma_bytes<false, false>(accB, r1[14], r2[14], r1[15], r2[15], breg[sub][14], breg[sub][15]);
+                mma_bytes<false, false>(accA, r1[16], r2[16], r1[17], r2[17], breg[sub][16], breg[sub][17]);
+                // columns: lane q=0 holds planes 0,1 of the first group, q=1 planes 2,3; q=2/3 the second group.
+                // Combine each lane's plane pair first, then one shuffle per row brings the upper pair over.
+                const uint32_t pair1 = (uint32_t)(accA[0] + accB[0]) + ((uint32_t)(accA[1] + accB[1]) << 8);
+                const uint32_t pair2 = (uint32_t)(accA[2] + accB[2]) + ((uint32_t)(accA[3] + accB[3]) << 8);
+                const uint32_t hi1 = __shfl_down_sync(0xffffffffu, pair1, 1);
+                const uint32_t hi2 = __shfl_down_sync(0xffffffffu, pair2, 1);
+                if (h == 0) {
+                    // 81 * (group sum) modulo 2^32, then times 81^-1 modulo 2^32: the exact integer group sum
+                    const int s1 = (int)((pair1 + (hi1 << 16) - (uint32_t)gsum[sub]) * 0x781948b1u);
+                    const int s2 = (int)((pair2 + (hi2 << 16) - (uint32_t)gsum[sub]) * 0x781948b1u);
+                    float dot1 = (float)s1 * gpow[sub];
+                    float dot2 = (float)s2 * gpow[sub];
+                    if (gbad[sub]) {
+                        const int group = sub + 2 * cls;
+                        const unsigned char *tile = ring + (warp * kStages + s) * kUnitBytes;
+                        const size_t x0 = ((size_t)c * kChunkGroups + group) * kGroup;
+                        dot1 = block_dot_fp32(tile + (g * kChunkGroups + group) * kBlockBytes, xh, xin, x0);
+                        dot2 = block_dot_fp32(tile + ((g + 8) * kChunkGroups + group) * kBlockBytes, xh, xin, x0);
+                    }
+                    const float sc1 = __half2float(__ushort_as_half((unsigned short)(w1a & 0xffffu)));
+                    const float sc2 = __half2float(__ushort_as_half((unsigned short)(w2a & 0xffffu)));
+                    acc1 = fmaf(sc1, dot1, acc1);
+                    acc2 = fmaf(sc2, dot2, acc2);
+                }
+            }
+            // the stage consumed one iteration ago is free: refill it
+            ++consumed;
+            __syncwarp();
+            if (lane == 0 && issued - consumed < kStages - 1) issue_one();
+
+            // quad: lanes q=0 (groups 0,1) and q=2 (groups 2,3) -> chunk partial in lane q=0
+            acc1 += __shfl_down_sync(0xffffffffu, acc1, 2);
+            acc2 += __shfl_down_sync(0xffffffffu, acc2, 2);
+            if (q == 0) {       // value and tag travel in one 64-bit store, so whoever sees the tag has the value
+                unsigned long long *mine = slots + ((size_t)c * tiles + t) * kTileRows;
+                slot_publish(mine + g, acc1, tag);
+                slot_publish(mine + g + 8, acc2, tag);
+            }
+            if (++t == tiles) { t = 0; ++c; }
+        }
+
+        // ---- finish row tiles ----------------------------------------------------------------------------
+        // Row tile t is finished by a fixed owner, the warp that processed its chunk t % chunks. The
+        // owner polls the tile's slots (bounded) until every chunk's value carries this link's tag. All
+        // CTAs of the grid are resident (one per SM), so the wait is for warps that are running. Lane
+        // (hf, r) adds chunks hf, hf+2, ... of row r in ascending order and one shuffle joins the two
+        // halves: the order of additions never depends on timing.
+        {
+            const int r = lane & 15, hf = lane >> 4;
+            const size_t stride = (size_t)tiles * kTileRows;
+            const bool swiglu = (flags & kFlagSwiglu) != 0;
+            const bool out_f32 = (flags & kFlagOutF32) != 0;
+            const float out_scale = L.out_scale;
+            void *y = L.y;
+            const int world = L.world;
+            int cc = R.c_first, tt = R.t_first;
+            for (int i = 0; i < n_units; ++i) {
+                if (tt % chunks == cc) {                 // warp-uniform: this warp owns row tile tt
+                    const unsigned long long *ps = slots + (size_t)tt * kTileRows + r;
+                    float total = 0.0f;
+                    for (int c0 = hf; c0 < chunks; c0 += 16) {
+                        unsigned long long v[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            v[k] = c0 + 2 * k < chunks ? slot_read(ps + (size_t)(c0 + 2 * k) * stride)
+                                                       : ((unsigned long long)tag << 32);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            if (c0 + 2 * k < chunks) {
+                                uint32_t spins = 0;
+                                while ((unsigned)(v[k] >> 32) != tag && !dead) {
+                                    if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 5u); dead = true; break; }
+                                    v[k] = slot_read(ps + (size_t)(c0 + 2 * k) * stride);
+                                }
+                                total += __uint_as_float((uint32_t)v[k]);
+                            }
+                        }
+                    }
+                    total += __shfl_xor_sync(0xffffffffu, total, 16);
+                    int row = tt * kTileRows + r;
+                    bool writer = hf == 0 && row < N;
+                    if (swiglu) {
+                        // rows come as (gate, up) pairs: the even lane of a pair holds silu(gate) * up
+                        const float up = __shfl_down_sync(0xffffffffu, total, 1);
+                        total = swiglu_f32(total, up);
+                        writer = writer && (r & 1) == 0 && row + 1 < N;
+                        row >>= 1;
+                    }
+                    total *= out_scale;
+                    if (writer) {
+                        const __half hv = __float2half_rn(total);
+                        if (y) {
+                            if (out_f32) static_cast<float *>(y)[row] = total;
+                            else static_cast<__half *>(y)[row] = hv;
+                        }
+                        // hand-off: the rounded FP16 value and this link's tag in one word, to every rank
+                        for (int pr = 0; pr < world; ++pr)
+                            word_publish(L.xout[pr] + row, (uint32_t)__half_as_ushort(hv), tag);
+                    }
+                }
+                if (++tt == tiles) { tt = 0; ++cc; }
+            }
+        }
+    }
+
+    // ---- leave: the last CTA resets the launch-scoped counters and moves the tag base on ----------------
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned prev = atomicAdd(ctl + kCtlExit, 1u);
+        if (prev == gridDim.x - 1) {
+            ctl[kCtlExit] = 0u;
+            ctl[kCtlArrive] = 0u;
+            ctl[kCtlArrive + 1] = 0u;
+            ctl[kCtlEpoch] = tag_base + P.tag_advance;
+        }
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// Per-device launch state: the shared-memory opt-in is an attribute of the function on ONE device.
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+    int sm_count;
+    bool attr_set;
+};
+DeviceState g_dev[kMaxDevices] = {};
+
+int device_state(DeviceState **out) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return cuda_fail(err, "tq1 chain: cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return fail(TQ1_ERR_INVALID, "tq1 chain: device %d out of range", dev);
+    DeviceState &st = g_dev[dev];
+    if (!st.attr_set) {
+        int sms = 0;
+        err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (err != cudaSuccess || sms <= 0) return cuda_fail(err, "tq1 chain: SM count");
+        err = cudaFuncSetAttribute(tq1_gemv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)(kWindowEnd + kHighBytes));
+        if (err != cudaSuccess) return cuda_fail(err, "tq1 chain: shared memory opt-in");
+        st.sm_count = sms;
+        st.attr_set = true;
+    }
+    *out = &st;
+    return TQ1_OK;
+}
+
+// A CTA keeps the digit planes of at most kMaxChunksPerCta chunks: check that no CTA of a grid of
+// `grid` CTAs spans more.
+bool span_ok(int tiles, int chunks, int grid) {
+    const unsigned total = (unsigned)tiles * (unsigned)chunks;
+    for (int b = 0; b < grid; ++b) {
+        const int begin = (int)(total * (unsigned)b / (unsigned)grid);
+        const int end = (int)(total * (unsigned)(b + 1) / (unsigned)grid);
+        if (end > begin && (end - 1) / tiles - begin / tiles + 1 > kMaxChunksPerCta) return false;
+    }
+    return true;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// Host side: turning caller-level links into kernel descriptors.
+
+bool gemv_chain_shape_ok(int N, int K) {
+    return N >= 1 && K >= kChunkCols && K % kChunkCols == 0 && K / kChunkCols <= 128;
+}
+
+bool gemv_chain_supported(const uint8_t *blocks, int N, int K) {
+    return gemv_chain_shape_ok(N, K) && (reinterpret_cast<uintptr_t>(blocks) & 15) == 0;
+}
+
+namespace {
+
+constexpr size_t kRegionSlotsTwo = kWsSlotRegionBytes / 2 / sizeof(unsigned long long);    // 1 Mi slots per region
+
+// Rows of one device link: its partial-sum slots (one per row and K chunk) must fit one region.
+int rows_per_link(int N, int K, size_t region_slots) {
+    const size_t chunks = K / kChunkCols;
+    const size_t cap = region_slots / chunks / kTileRows * kTileRows;
+    if ((size_t)N <= cap) return N;
+    const size_t parts = ((size_t)N + cap - 1) / cap;
+    return (int)((((size_t)N + parts - 1) / parts + kTileRows - 1) / kTileRows * kTileRows);
+}
+
+int encode_link_map(CUtensorMap *map, const uint8_t *blocks, int N, int K) {
+    EncodeTiledFn encode = encode_fn();
+    if (!encode) return fail(TQ1_ERR_CUDA, "tq1 chain: cuTensorMapEncodeTiled is unavailable");
+    const cuuint64_t row_bytes = (cuuint64_t)(K / kGroup) * kBlockBytes;
+    const cuuint64_t dims[2] = {row_bytes, (cuuint64_t)N};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {kChunkBytes, kTileRows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult res = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(blocks), dims, strides, box,
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_SUCCESS) return fail(TQ1_ERR_CUDA, "tq1 chain: cuTensorMapEncodeTiled failed (%d)", (int)res);
+    return TQ1_OK;
+}
+
+size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+// Output elements of a caller-level link on one rank, and gathered over the ranks.
+int link_out_local(const tq1_chain_link &l) { return l.swiglu ? l.N / 2 : l.N; }
+
+}  // namespace
+
+size_t gemv_chain_handoff_bytes(const tq1_chain_link *links, int n_links, int world) {
+    size_t total = 0;
+    for (int i = 0; i < n_links; ++i)
+        total += align256((size_t)link_out_local(links[i]) * (size_t)(world < 1 ? 1 : world) * sizeof(unsigned long long));
+    return total;
+}
+
+int gemv_chain_device_links(const tq1_chain_link *links, int n_links, size_t region_slots) {
+    int total = 0;
+    for (int i = 0; i < n_links; ++i) {
+        if (links[i].K <= 0 || links[i].K % kChunkCols) return -1;
+        const int step = rows_per_link(links[i].N, links[i].K, region_slots);
+        total += (links[i].N + step - 1) / step;
+    }
+    return total;
+}
+
+// Fills `out` (host memory, gemv_chain_device_links() entries). handoff[r] is rank r's hand-off area
+// (the local one for rank == r); each caller-level link owns a 256-byte aligned range of it that holds
+// the gathered output, one 64-bit word per element.
+int gemv_chain_describe(const tq1_chain_link *links, int n_links, int rank, int world,
+                        unsigned long long *const *handoff, size_t region_slots, int grid,
+                        std::vector<ChainLinkDev> &out) {
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+        return fail(TQ1_ERR_INVALID, "tq1 chain: rank %d of %d is out of range (at most %d ranks)", rank, world, kMaxRanks);
+    std::vector<size_t> offset(n_links);          // in words
+    std::vector<bool> consumed(n_links, false);
+    size_t cursor = 0;
+    for (int i = 0; i < n_links; ++i) {
+        offset[i] = cursor;
+        cursor += align256((size_t)link_out_local(links[i]) * world * sizeof(unsigned long long)) / sizeof(unsigned long long);
+        if (!links[i].x) {
+            if (links[i].source < 0 || links[i].source >= i)
+                return fail(TQ1_ERR_INVALID, "tq1 chain: link %d reads link %d, which does not precede it", i, links[i].source);
+            consumed[links[i].source] = true;
+        }
+    }
+    out.clear();
+    for (int i = 0; i < n_links; ++i) {
+        const tq1_chain_link &l = links[i];
+        if (!l.blocks) return fail(TQ1_ERR_INVALID, "tq1 chain: link %d has no weights", i);
+        if (!gemv_chain_supported(l.blocks, l.N, l.K))
+            return fail(TQ1_ERR_INVALID,
+                        "tq1 chain: link %d (%dx%d) needs K %% 512 == 0, at most 128 K chunks and 16-byte aligned blocks",
+                        i, l.N, l.K);
+        if (l.swiglu && (l.N % 2))
+            return fail(TQ1_ERR_INVALID, "tq1 chain: link %d: %d rows cannot be (gate, up) pairs", i, l.N);
+        if (world > 1 && (l.N % kTileRows))
+            return fail(TQ1_ERR_INVALID, "tq1 chain: link %d: a shard of %d rows is not a multiple of %d", i, l.N, kTileRows);
+        const unsigned long long *xin = nullptr;
+        if (!l.x) {
+            const tq1_chain_link &s = links[l.source];
+            const long long have = (long long)link_out_local(s) * world;
+            if (l.source_offset < 0 || (long long)l.source_offset + l.K > have)
+                return fail(TQ1_ERR_INVALID, "tq1 chain: link %d reads elements [%d, %d) of link %d, which has %lld",
+                            i, l.source_offset, l.source_offset + l.K, l.source, have);
+            if (!handoff || !handoff[rank]) return fail(TQ1_ERR_INVALID, "tq1 chain: no hand-off area");
+            xin = handoff[rank] + offset[l.source] + l.source_offset;
+        }
+        const int step = rows_per_link(l.N, l.K, region_slots);
+        if (step < l.N && l.swiglu && (step % 2))
+            return fail(TQ1_ERR_INVALID, "tq1 chain: link %d cannot be split into row ranges", i);
+        const size_t row_bytes = (size_t)(l.K / kGroup) * kBlockBytes;
+        const int out_local = link_out_local(l);
+        for (int n0 = 0; n0 < l.N; n0 += step) {
+            const int rows = l.N - n0 < step ? l.N - n0 : step;
+            ChainLinkDev d;
+            memset(&d, 0, sizeof(d));
+            int rc = encode_link_map(&d.wmap, l.blocks + (size_t)n0 * row_bytes, rows, l.K);
+            if (rc != TQ1_OK) return rc;
+            d.x = static_cast<const __half *>(l.x);
+            d.xin = xin;
+            const int out0 = l.swiglu ? n0 / 2 : n0;
+            if (l.y)
+                d.y = l.y_is_f32 ? static_cast<void *>(static_cast<float *>(l.y) + out0)
+                                 : static_cast<void *>(static_cast<__half *>(l.y) + out0);
+            d.N = rows;
+            d.K = l.K;
+            d.tiles = (rows + kTileRows - 1) / kTileRows;
+            d.chunks = l.K / kChunkCols;
+            if (!span_ok(d.tiles, d.chunks, grid))
+                return fail(TQ1_ERR_INVALID, "tq1 chain: link %d (%dx%d) spreads a CTA over more than %d K chunks",
+                            i, l.N, l.K, kMaxChunksPerCta);
+            d.src_tag = l.x ? 0 : l.source;
+            d.tag = i;
+            d.flags = (l.y_is_f32 ? kFlagOutF32 : 0u) | (l.swiglu ? kFlagSwiglu : 0u);
+            d.out_scale = l.out_scale == 0.0f ? 1.0f : l.out_scale;
+            d.world = 0;
+            if (consumed[i] || world > 1) {
+                if (!handoff) return fail(TQ1_ERR_INVALID, "tq1 chain: no hand-off area");
+                d.world = world;
+                for (int pr = 0; pr < world; ++pr) {
+                    if (!handoff[pr]) return fail(TQ1_ERR_INVALID, "tq1 chain: no hand-off area for rank %d", pr);
+                    d.xout[pr] = handoff[pr] + offset[i] + (size_t)rank * out_local + out0;
+                }
+            }
+            out.push_back(d);
+        }
+    }
+    return TQ1_OK;
+}
+
+int gemv_chain_launch(const ChainLinkDev *table_dev, const ChainLinkDev *inline_links, int n_dev_links,
+                      unsigned tag_advance, void *workspace, size_t region_slots, int n_regions,
+                      cudaStream_t stream) {
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc != TQ1_OK) return rc;
+    ChainParams params;
+    memset(&params, 0, sizeof(params));
+    params.table = table_dev;
+    unsigned char *ws = static_cast<unsigned char *>(workspace);
+    params.ctl = reinterpret_cast<unsigned *>(ws);
+    params.slots = reinterpret_cast<unsigned long long *>(ws + kWsStatusBytes);
+    params.region_slots = region_slots;
+    params.n_links = n_dev_links;
+    params.n_regions = n_regions;
+    params.tag_advance = tag_advance;
+    if (!table_dev) {
+        if (n_dev_links > kInlineLinks)
+            return fail(TQ1_ERR_INVALID, "tq1 chain: %d links do not fit a launch without a plan (at most %d)",
+                        n_dev_links, kInlineLinks);
+        memcpy(params.inl, inline_links, sizeof(ChainLinkDev) * n_dev_links);
+    }
+    static const bool use_pdl = getenv("TQ1_DISABLE_PDL") == nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)st->sm_count);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kWindowEnd + kHighBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, tq1_gemv_chain_kernel, params);
+    if (err != cudaSuccess) return cuda_fail(err, "tq1 chain: launch");
+    return TQ1_OK;
+}
+
+int gemv_chain_grid(int *grid) {
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc != TQ1_OK) return rc;
+    *grid = st->sm_count;
+    return TQ1_OK;
+}
+
+size_t gemv_chain_region_slots() { return kRegionSlotsTwo; }
+size_t gemv_chain_link_bytes() { return sizeof(ChainLinkDev); }
+
+// One product through the chain kernel (a chain of one link per row range).
+int launch_gemv_single(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K, bool swiglu,
+                       void *workspace, size_t slot_bytes, cudaStream_t stream) {
+    int grid = 0;
+    int rc = gemv_chain_grid(&grid);
+    if (rc != TQ1_OK) return rc;
+    // single links never run ahead of one another inside a launch, so one region holds all the slots
+    const size_t region_slots = slot_bytes / sizeof(unsigned long long);
+    tq1_chain_link l;
+    memset(&l, 0, sizeof(l));
+    l.blocks = blocks; l.N = N; l.K = K; l.x = x; l.y = y; l.y_is_f32 = y_f32; l.swiglu = swiglu; l.out_scale = 1.0f;
+    std::vector<ChainLinkDev> dev;
+    rc = gemv_chain_describe(&l, 1, 0, 1, nullptr, region_slots, grid, dev);
+    if (rc != TQ1_OK) return rc;
+    for (size_t i = 0; i < dev.size(); ++i) {          // row ranges of a very tall matrix: one launch each
+        dev[i].tag = 0;
+        rc = gemv_chain_launch(nullptr, &dev[i], 1, 1u, workspace, region_slots, 1, stream);
+        if (rc != TQ1_OK) return rc;
+    }
+    return TQ1_OK;
+}
+
+
+// Whether the chain kernel takes one product of this shape on the current device.
+bool gemv_chain_fits(const uint8_t *blocks, int N, int K) {
+    if (!gemv_chain_supported(blocks, N, K)) return false;
+    int grid = 0;
+    if (gemv_chain_grid(&grid) != TQ1_OK) return false;
+    const int rows = rows_per_link(N, K, kWsSlotRegionBytes / sizeof(unsigned long long));
+    return span_ok((rows + kTileRows - 1) / kTileRows, K / kChunkCols, grid);
+}
+
+size_t gemv_chain_workspace_bytes(int N, int K) {
+    const size_t rows = rows_per_link(N, K, kWsSlotRegionBytes / sizeof(unsigned long long));
+    const size_t tiles = (rows + kTileRows - 1) / kTileRows;
+    return kWsStatusBytes + (size_t)(K / kChunkCols) * tiles * kTileRows * sizeof(unsigned long long);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the batch-1 GEMV.
+//
+// Some hosts cannot give this library scratch memory at call time: code that runs inside a
+// stream-capture region (where cudaMalloc is illegal), plugin hosts whose whole device budget
+// was handed out when the model was loaded, and real-time loops that must not touch the
+// allocator. For them the scratch of the GEMV (control words and per-chunk partial-sum slots)
+// lives in this fixed array, which every GPU that loads the library holds until the process
+// exits.
+constexpr size_t kNoAllocScratchBytes = 2u << 20;       // 2 MiB: N*K up to about 1.3e8 weights
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+namespace {
+void *g_noalloc_ptr[kMaxDevices] = {};     // device address of g_noalloc_scratch, per device
+
+int noalloc_scratch(void **out, const char *who) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return cuda_fail(err, who);
+    if (dev < 0 || dev >= kMaxDevices) return fail(TQ1_ERR_INVALID, "%s: device %d out of range", who, dev);
+    if (!g_noalloc_ptr[dev]) {
+        // In host code the array's name is only a handle; the kernel needs its device address. The
+        // array starts zero-filled (static storage) and the kernel never needs it cleared again.
+        void *ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (err != cudaSuccess) return cuda_fail(err, who);
+        g_noalloc_ptr[dev] = ptr;
+    }
+    *out = g_noalloc_ptr[dev];
+    return TQ1_OK;
+}
+}  // namespace
+
+int gemv_noalloc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K, cudaStream_t stream) {
+    if (!gemv_chain_supported(blocks, N, K))
+        return fail(TQ1_ERR_INVALID,
+                    "tq1_gemv_f16_noalloc: needs K %% 512 == 0, at most 128 K chunks and 16-byte aligned blocks "
+                    "(got N=%d K=%d)", N, K);
+    const size_t slot_bytes = kNoAllocScratchBytes - kWsStatusBytes;
+    const size_t need = (size_t)(K / kChunkCols) * ((N + kTileRows - 1) / kTileRows) * kTileRows * sizeof(unsigned long long);
+    if (need > slot_bytes)
+        return fail(TQ1_ERR_WORKSPACE,
+                    "tq1_gemv_f16_noalloc: %dx%d needs %zu bytes of scratch, the built-in array holds %zu",
+                    N, K, need + kWsStatusBytes, (size_t)kNoAllocScratchBytes);
+    void *scratch = nullptr;
+    int rc = noalloc_scratch(&scratch, "tq1_gemv_f16_noalloc");
+    if (rc != TQ1_OK) return rc;
+    return launch_gemv_single(blocks, x, y, y_f32, N, K, false, scratch, slot_bytes, stream);
+}
+
+int gemv_noalloc_status(unsigned *out_host, cudaStream_t stream) {
+    void *scratch = nullptr;
+    int rc = noalloc_scratch(&scratch, "tq1_gemv_noalloc_status");
+    if (rc != TQ1_OK) return rc;
+    cudaError_t err = cudaMemcpyAsync(out_host, scratch, sizeof(unsigned), cudaMemcpyDeviceToHost, stream);
+    if (err != cudaSuccess) return cuda_fail(err, "tq1_gemv_noalloc_status");
+    return TQ1_OK;
+}
+
+}  // namespace tq1
+
+// ---------------------------------------------------------------------------------------------
+// C ABI of the chain (declared in include/ternel_b200.h).
+
+using namespace tq1;
+
+struct tq1_chain_plan {
+    std::vector<ChainLinkDev> host;     // what was uploaded (kept so the upload's source outlives the copy)
+    const ChainLinkDev *table_dev;
+    void *workspace;
+    int n_dev_links;
+    int n_links;
+};
+
+extern "C" {
+
+size_t tq1_chain_handoff_bytes(const tq1_chain_link *links, int n_links, int world) {
+    if (!links || n_links <= 0) return 0;
+    return gemv_chain_handoff_bytes(links, n_links, world);
+}
+
+size_t tq1_chain_workspace_bytes(const tq1_chain_link *links, int n_links, int world) {
+    if (!links || n_links <= 0) return 0;
+    // control words, two slot regions, and (single GPU) the hand-off words behind them
+    return kWsScratchOffset + (world <= 1 ? gemv_chain_handoff_bytes(links, n_links, 1) : 0);
+}
+
+size_t tq1_chain_table_bytes(const tq1_chain_link *links, int n_links) {
+    if (!links || n_links <= 0) return 0;
+    const int n = gemv_chain_device_links(links, n_links, gemv_chain_region_slots());
+    return n <= 0 ? 0 : (size_t)n * sizeof(ChainLinkDev);
+}
+
+static int chain_describe_checked(const tq1_chain_link *links, int n_links, const tq1_chain_peers *peers,
+                                  void *workspace, size_t workspace_bytes, std::vector<ChainLinkDev> &dev) {
+    if (!links || n_links <= 0) return fail(TQ1_ERR_INVALID, "tq1 chain: no links");
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255))
+        return fail(TQ1_ERR_WORKSPACE, "tq1 chain: a 256-byte aligned workspace is required");
+    const int world = peers ? peers->world : 1;
+    const int rank = peers ? peers->rank : 0;
+    const size_t need = tq1_chain_workspace_bytes(links, n_links, world);
+    if (workspace_bytes < need)
+        return fail(TQ1_ERR_WORKSPACE, "tq1 chain: workspace of %zu bytes required, got %zu", need, workspace_bytes);
+    unsigned long long *areas[kMaxRanks] = {};
+    if (peers) {
+        if (world < 1 || world > kMaxRanks) return fail(TQ1_ERR_INVALID, "tq1 chain: world size %d", world);
+        for (int r = 0; r < world; ++r) {
+            if (!peers->handoff[r] || (reinterpret_cast<uintptr_t>(peers->handoff[r]) & 255))
+                return fail(TQ1_ERR_INVALID, "tq1 chain: hand-off area of rank %d missing or not 256-byte aligned", r);
+            areas[r] = static_cast<unsigned long long *>(peers->handoff[r]);
+        }
+    } else {
+        areas[0] = reinterpret_cast<unsigned long long *>(static_cast<unsigned char *>(workspace) + kWsScratchOffset);
+    }
+    int grid = 0;
+    int rc = gemv_chain_grid(&grid);
+    if (rc != TQ1_OK) return rc;
+    return gemv_chain_describe(links, n_links, rank, world, areas, gemv_chain_region_slots(), grid, dev);
+}
+
+int tq1_chain_plan_create(const tq1_chain_link *links, int n_links, const tq1_chain_peers *peers,
+                          void *workspace, size_t workspace_bytes, void *table, size_t table_bytes,
+                          void *stream, tq1_chain_plan **out) {
+    if (!out) return fail(TQ1_ERR_INVALID, "tq1_chain_plan_create: null pointer");
+    *out = nullptr;
+    tq1_chain_plan *plan = new (std::nothrow) tq1_chain_plan();
+    if (!plan) return fail(TQ1_ERR_INVALID, "tq1_chain_plan_create: out of host memory");
+    int rc = chain_describe_checked(links, n_links, peers, workspace, workspace_bytes, plan->host);
+    if (rc != TQ1_OK) { delete plan; return rc; }
+    const size_t bytes = plan->host.size() * sizeof(ChainLinkDev);
+    if (!table || table_bytes < bytes || (reinterpret_cast<uintptr_t>(table) & 127)) {
+        delete plan;
+        return fail(TQ1_ERR_WORKSPACE, "tq1_chain_plan_create: a 128-byte aligned device table of %zu bytes is required", bytes);
+    }
+    cudaError_t err = cudaMemcpyAsync(table, plan->host.data(), bytes, cudaMemcpyHostToDevice,
+                                      static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) { delete plan; return cuda_fail(err, "tq1_chain_plan_create: table upload"); }
+    plan->table_dev = static_cast<const ChainLinkDev *>(table);
+    plan->workspace = workspace;
+    plan->n_dev_links = (int)plan->host.size();
+    plan->n_links = n_links;
+    *out = plan;
+    return TQ1_OK;
+}
+
+int tq1_chain_plan_run(const tq1_chain_plan *plan, void *stream) {
+    if (!plan) return fail(TQ1_ERR_INVALID, "tq1_chain_plan_run: null plan");
+    return gemv_chain_launch(plan->table_dev, nullptr, plan->n_dev_links, (unsigned)plan->n_links, plan->workspace,
+                             gemv_chain_region_slots(), 2, static_cast<cudaStream_t>(stream));
+}
+
+void tq1_chain_plan_destroy(tq1_chain_plan *plan) { delete plan; }
+
+int tq1_linear_chain_f16(const tq1_chain_link *links, int n_links, void *workspace, size_t workspace_bytes,
+                         void *stream) {
+    std::vector<ChainLinkDev> dev;
+    int rc = chain_describe_checked(links, n_links, nullptr, workspace, workspace_bytes, dev);
+    if (rc != TQ1_OK) return rc;
+    return gemv_chain_launch(nullptr, dev.data(), (int)dev.size(), (unsigned)n_links, workspace,
+                             gemv_chain_region_slots(), 2, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

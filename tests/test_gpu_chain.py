@@ -1,0 +1,220 @@
+"""Chains of batch-1 products in one persistent launch: every link against the oracle, fed with the
+activations the GPU actually handed over, plus the bookkeeping that lets a chain be replayed. Needs a B200."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import tq1_oracle as o
+from tests.gpu_util import random_blocks, to_dev
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5          # FP32 output, the reference's own bound (src/ternel_mlx/kernel_gate.py:105)
+
+
+def silu_mul(gate, up):
+    gate = gate.astype(np.float32)
+    return gate / (np.float32(1.0) + np.exp(-gate)) * up.astype(np.float32)
+
+
+def oracle_link(blocks, x, *, swiglu=False, out_scale=1.0):
+    rows, columns = blocks.shape[0], blocks.shape[1] * 128
+    y = o.float64_matmul(blocks, x.astype(np.float32)[None, :], rows=rows, columns=columns)[0]
+    if swiglu:
+        y = silu_mul(y[0::2], y[1::2])
+    return (y * np.float32(out_scale)).astype(np.float32)
+
+
+def check_chain(specs, x0, *, plan=True, repeats=2):
+    """specs: list of dicts(blocks, source, source_offset, swiglu, out_scale, x). Runs the chain, then checks each
+    link against the oracle applied to the FP16 values the GPU produced for its source."""
+    from ternel_b200.chain import ChainPlan, Link, chain_workspace_bytes, linear_chain
+
+    links, outs32, outs16 = [], [], []
+    for spec in specs:
+        blocks = spec["blocks"]
+        n_out = blocks.shape[0] // 2 if spec.get("swiglu") else blocks.shape[0]
+        y32 = torch.full((n_out,), float("nan"), dtype=torch.float32, device="cuda")
+        outs32.append(y32)
+        links.append(Link(blocks=to_dev(blocks),
+                          x=to_dev(spec["x"].astype(np.float16)) if spec.get("x") is not None else None,
+                          source=spec.get("source", -1), source_offset=spec.get("source_offset", 0), y=y32,
+                          swiglu=bool(spec.get("swiglu")), out_scale=spec.get("out_scale", 1.0)))
+    if plan:
+        runner = ChainPlan(links)
+        run = runner.run
+        workspace = runner.workspace
+    else:
+        workspace = torch.zeros(chain_workspace_bytes(links), dtype=torch.uint8, device="cuda")
+        run = lambda: linear_chain(links, workspace)
+    first = None
+    for _ in range(repeats):
+        for y in outs32:
+            y.fill_(float("nan"))
+        run()
+        torch.cuda.synchronize()
+        assert int(workspace[:4].view(torch.int32)[0].item()) == 0, "a bounded device wait ran out"
+        got = [y.cpu().numpy() for y in outs32]
+        if first is None:
+            first = got
+        else:                               # replays are bit-identical
+            for a, b in zip(first, got):
+                assert np.array_equal(a, b)
+    for i, spec in enumerate(specs):
+        if spec.get("x") is not None:
+            x = spec["x"].astype(np.float16)
+        else:
+            src = first[spec["source"]].astype(np.float16)      # what the next link was handed: the FP16 rounding
+            k = spec["blocks"].shape[1] * 128
+            x = src[spec.get("source_offset", 0): spec.get("source_offset", 0) + k]
+        want = oracle_link(spec["blocks"], x, swiglu=bool(spec.get("swiglu")), out_scale=spec.get("out_scale", 1.0))
+        err = o.normalised_error(first[i][None, :], want[None, :])
+        assert err < F32_TOL, f"link {i}: {err}"
+    return first
+
+
+def test_single_link_equals_the_plain_entry_point():
+    from ternel_b200.ops import tq1_matmul
+    blocks, rng = random_blocks(1024, 5120, seed=3)
+    x = rng.standard_normal(5120).astype(np.float16)
+    got = check_chain([dict(blocks=blocks, x=x)], x, plan=False)[0]
+    plain = tq1_matmul(to_dev(blocks), to_dev(x[None, :]), out_dtype=torch.float32).cpu().numpy()[0]
+    assert np.array_equal(got, plain)
+
+
+@pytest.mark.parametrize("plan", (False, True))
+def test_dependent_links_hand_their_output_over(plan):
+    """qkv -> o (reads the q part) -> gate|up with SiLU*mul -> down, each reading its predecessor."""
+    hidden, ffn = 1024, 1536
+    rng = np.random.default_rng(5)
+    qkv, _ = random_blocks(hidden + 512, hidden, seed=11)
+    wo, _ = random_blocks(hidden, hidden, seed=12)
+    gate_up, _ = random_blocks(2 * ffn, hidden, seed=13)
+    down, _ = random_blocks(hidden, ffn, seed=14)
+    x = rng.standard_normal(hidden).astype(np.float16)
+    specs = [
+        dict(blocks=qkv, x=x, out_scale=2.0),
+        dict(blocks=wo, source=0, source_offset=0, out_scale=1.5),
+        dict(blocks=gate_up, source=1, swiglu=True, out_scale=4.0),
+        dict(blocks=down, source=2, out_scale=0.5),
+    ]
+    check_chain(specs, x, plan=plan, repeats=3)
+
+
+def test_two_layers_of_model_shapes_in_one_plan():
+    """Eight links shaped like two decoder layers (scaled down): every link depends on the one before."""
+    hidden, ffn, kv = 1536, 4608, 256
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal(hidden).astype(np.float16)
+    specs = []
+    for layer in range(2):
+        qkv, _ = random_blocks(hidden + 2 * kv, hidden, seed=100 + layer)
+        wo, _ = random_blocks(hidden, hidden, seed=200 + layer)
+        gate_up, _ = random_blocks(2 * ffn, hidden, seed=300 + layer)
+        down, _ = random_blocks(hidden, ffn, seed=400 + layer)
+        base = 4 * layer
+        specs += [
+            dict(blocks=qkv, out_scale=1.0 / 0.45, **(dict(x=x) if layer == 0 else dict(source=base - 1))),
+            dict(blocks=wo, source=base, out_scale=1.0 / 0.45),
+            dict(blocks=gate_up, source=base + 1, swiglu=True, out_scale=6.0),
+            dict(blocks=down, source=base + 2, out_scale=1.0 / 0.8),
+        ]
+    check_chain(specs, x, plan=True, repeats=2)
+
+
+def test_fan_out_and_independent_links():
+    """Three links read the same earlier output, two more read activations that exist before the launch."""
+    rng = np.random.default_rng(21)
+    first, _ = random_blocks(1536, 1024, seed=31)
+    a, _ = random_blocks(512, 1536, seed=32)
+    b, _ = random_blocks(48, 1536, seed=33)            # N not a multiple of 16
+    c, _ = random_blocks(2000, 1024, seed=34)
+    d, _ = random_blocks(300, 512, seed=35)
+    x = rng.standard_normal(1024).astype(np.float16)
+    x2 = rng.standard_normal(512).astype(np.float16)
+    specs = [
+        dict(blocks=first, x=x),
+        dict(blocks=a, source=0),
+        dict(blocks=b, source=0),
+        dict(blocks=c, source=0, source_offset=512),
+        dict(blocks=d, x=x2),
+        dict(blocks=c, x=x),
+    ]
+    check_chain(specs, x, plan=True, repeats=2)
+    check_chain(specs, x, plan=False, repeats=2)
+
+
+def test_many_links_reuse_both_slot_regions():
+    """Sixteen dependent square links: the two slot regions alternate and the arrival counters gate the reuse."""
+    size = 1024
+    rng = np.random.default_rng(40)
+    x = rng.standard_normal(size).astype(np.float16)
+    specs = []
+    for i in range(16):
+        blocks, _ = random_blocks(size, size, seed=500 + i)
+        specs.append(dict(blocks=blocks, out_scale=1.0 / 0.4, **(dict(x=x) if i == 0 else dict(source=i - 1))))
+    check_chain(specs, x, plan=True, repeats=3)
+
+
+def test_non_finite_values_travel_through_the_hand_off():
+    blocks0, _ = random_blocks(1024, 1024, seed=61, dist="tests")
+    blocks1, _ = random_blocks(512, 1024, seed=62, dist="tests")
+    x = np.random.default_rng(2).standard_normal(1024).astype(np.float16)
+    x[77] = np.inf
+    from ternel_b200.chain import ChainPlan, Link
+    y0 = torch.zeros(1024, dtype=torch.float32, device="cuda")
+    y1 = torch.zeros(512, dtype=torch.float32, device="cuda")
+    plan = ChainPlan([Link(blocks=to_dev(blocks0), x=to_dev(x), y=y0), Link(blocks=to_dev(blocks1), source=0, y=y1)])
+    plan.run()
+    torch.cuda.synchronize()
+    assert plan.status() == 0
+    with np.errstate(invalid="ignore", over="ignore"):
+        want0 = o.reference_matmul(blocks0, x.astype(np.float32)[None, :], rows=1024, columns=1024)
+        got0 = y0.cpu().numpy()[None, :]
+        assert np.array_equal(o.nonfinite_classes(got0), o.nonfinite_classes(want0))
+        want1 = o.reference_matmul(blocks1, got0.astype(np.float16).astype(np.float32), rows=512, columns=1024)
+    assert np.array_equal(o.nonfinite_classes(y1.cpu().numpy()[None, :]), o.nonfinite_classes(want1))
+
+
+def test_chain_shares_its_workspace_with_single_calls():
+    """Single batch-1 calls through the C ABI on the chain's workspace between replays of the chain."""
+    import ctypes
+    from ternel_b200 import _native
+    from ternel_b200.chain import ChainPlan, Link
+    from ternel_b200.format import check
+    lib = _native.lib()
+    blocks0, rng = random_blocks(1024, 1024, seed=71)
+    blocks1, _ = random_blocks(768, 1024, seed=72)
+    x = rng.standard_normal(1024).astype(np.float16)
+    y0 = torch.zeros(1024, dtype=torch.float32, device="cuda")
+    y1 = torch.zeros(768, dtype=torch.float32, device="cuda")
+    xd, b0, b1 = to_dev(x), to_dev(blocks0), to_dev(blocks1)
+    plan = ChainPlan([Link(blocks=b0, x=xd, y=y0), Link(blocks=b1, source=0, y=y1)])
+    plan.run()
+    torch.cuda.synchronize()
+    first = y1.cpu().numpy().copy()
+    single = torch.zeros(1024, dtype=torch.float32, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for _ in range(3):
+        check(lib.tq1_linear_f16(b0.data_ptr(), xd.data_ptr(), single.data_ptr(), 1, 1, 1024, 1024,
+                                 plan.workspace.data_ptr(), plan.workspace.numel(), stream))
+        plan.run()
+        torch.cuda.synchronize()
+        assert np.array_equal(single.cpu().numpy(), y0.cpu().numpy())
+        assert np.array_equal(y1.cpu().numpy(), first)
+    assert plan.status() == 0
+
+
+def test_bad_links_are_refused_before_any_launch():
+    from ternel_b200.chain import ChainPlan, Link
+    from ternel_b200.format import FormatError
+    blocks, rng = random_blocks(256, 1024, seed=81)
+    x = to_dev(rng.standard_normal(1024).astype(np.float16))
+    b = to_dev(blocks)
+    with pytest.raises(FormatError):
+        ChainPlan([Link(blocks=b, source=0)])                              # the first link has nothing to read
+    with pytest.raises((FormatError, ValueError)):
+        ChainPlan([Link(blocks=b, x=x), Link(blocks=b, source=0)])         # 256 outputs cannot feed K = 1024
+    with pytest.raises((FormatError, ValueError)):
+        ChainPlan([Link(blocks=to_dev(random_blocks(256, 640, seed=1)[0]), x=x[:640].contiguous())])   # K % 512

@@ -18,7 +18,7 @@ from tests.conftest import GOLDEN, ROOT
 
 def test_library_exports_every_declared_symbol():
     header = (ROOT / "include" / "ternel_b200.h").read_text()
-    declared = set(re.findall(r"^(?:int|size_t|const char \*)\s*(tq1_[a-z0-9_]+)\s*\(", header, re.M))
+    declared = set(re.findall(r"^(?:int|void|size_t|const char \*)\s*(tq1_[a-z0-9_]+)\s*\(", header, re.M))
     assert declared, "no declarations found"
     assert declared == set(_native.SIGNATURES), declared ^ set(_native.SIGNATURES)
     handle = ctypes.CDLL(str(_native.LIB_PATH))

@@ -14,6 +14,7 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import tq1_oracle as o
 from tests.gpu_util import random_blocks
 
 pytestmark = pytest.mark.gpu
@@ -49,6 +50,14 @@ def test_no_alloc_entry_matches_the_regular_entry_twice_in_a_row():
             # same kernel, same summation order: the two entry points agree bit for bit
             assert np.array_equal(got, want), (rows, columns, call)
             assert np.isfinite(got).all() and np.abs(got).max() > 0
+            # and both agree with the float64 oracle (FP32 out: the reference's 1e-5; after an FP16 store: 2e-3)
+            exact = o.float64_matmul(blocks, x, rows=rows, columns=columns)
+            assert o.normalised_error(got, exact) < (1e-5 if out_f32 else 2e-3), (rows, columns, call)
+    # no bounded wait ran out in any of those calls: the array's status word is still zero
+    status = np.full(1, 99, dtype=np.uint32)
+    assert lib.tq1_gemv_noalloc_status(status.ctypes.data, None) == 0, _native.last_error()
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
 
 
 def test_no_alloc_entry_refuses_what_does_not_fit():
