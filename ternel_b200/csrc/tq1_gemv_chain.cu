@@ -60,12 +60,19 @@ constexpr int kChunkGroups = 4;
 constexpr int kChunkCols = kChunkGroups * kGroup;             // 512
 constexpr int kChunkBytes = kChunkGroups * kBlockBytes;       // 112
 constexpr int kUnitBytes = kTileRows * kChunkBytes;           // 1792
-constexpr int kStages = 4;
-constexpr int kWarps = 16;
+#ifndef TQ1_GEMV_WARPS
+#define TQ1_GEMV_WARPS 16
+#endif
+#ifndef TQ1_GEMV_STAGES
+#define TQ1_GEMV_STAGES 4
+#endif
+constexpr int kStages = TQ1_GEMV_STAGES;
+constexpr int kWarps = TQ1_GEMV_WARPS;           // the first 16 also prepare the activations (one thread each)
+constexpr int kPrepThreads = 512;
 constexpr int kThreads = kWarps * 32;
 constexpr int kMaxChunksPerCta = 3;
 constexpr int kRegsPerSub = 18;                                // A/B registers per lane per sub-unit
-static_assert((kStages & (kStages - 1)) == 0, "stage index is taken with a mask");
+static_assert(kWarps >= 16, "sixteen warps prepare the activations");
 
 // Shared-memory window layout (addresses relative to the CTA's shared window). The table sits
 // at a 64 KiB multiple so that PRMT can build a complete lookup address
@@ -78,7 +85,7 @@ constexpr uint32_t kRingBytes = kWarps * kStages * kUnitBytes;                  
 constexpr uint32_t kBtabOne = kMaxChunksPerCta * 2 * kRegsPerSub * 32 * 4;         // 13824 per buffer
 constexpr uint32_t kBtabBytes = 2 * kBtabOne;                                      // two links in flight
 constexpr uint32_t kMbarBytes = 8 * (kWarps * kStages + 2);
-constexpr uint32_t kRedOne = 3 * 4 * kWarps * kMaxChunksPerCta;                    // group max / sum / non-finite
+constexpr uint32_t kRedOne = 3 * 4 * 16 * kMaxChunksPerCta;                        // group max / sum / non-finite
 constexpr uint32_t kRedBytes = 2 * kRedOne;
 constexpr uint32_t kHighBytes = kBtabBytes + kMbarBytes + kRedBytes;
 static_assert(kRingBytes + 1024 + 128 <= kLutWindowAddr, "the ring must end below the table's fixed address");
@@ -91,6 +98,20 @@ constexpr int kCtlExit = 1;        // CTAs that have left the current launch
 constexpr int kCtlEpoch = 2;       // links executed by all earlier launches on this workspace (tag base)
 constexpr int kCtlArrive = 3;      // [2] CTAs that are done with the slots of the links of each region
 
+// Optional phase timers (build with -DTQ1_PHASE_TIMERS): lane 0 of every warp of the first CTAs accumulates
+// clock cycles per phase of a link; tq1_debug_read_phases() copies them out.
+#ifdef TQ1_PHASE_TIMERS
+constexpr int kPhases = 8;
+__device__ long long g_phase_acc[64 * kWarps * kPhases];
+#define PHASE_DECL long long ph_t = clock64(), ph_acc[kPhases] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define PHASE(i) { const long long now_ = clock64(); ph_acc[i] += now_ - ph_t; ph_t = now_; }
+#define PHASE_DUMP if (lane == 0 && blockIdx.x < 64) { for (int i_ = 0; i_ < kPhases; ++i_) g_phase_acc[(blockIdx.x * kWarps + warp) * kPhases + i_] = ph_acc[i_]; }
+#else
+#define PHASE_DECL
+#define PHASE(i)
+#define PHASE_DUMP
+#endif
+
 constexpr unsigned kFlagOutF32 = 1u;
 constexpr unsigned kFlagSwiglu = 2u;
 
@@ -102,13 +123,13 @@ struct alignas(128) ChainLinkDev {
     void *y;                                    // FP16/FP32 output, or null
     unsigned long long *xout[kMaxRanks];        // per rank: hand-off words of this link's output, at this rank's first
                                                 // output element (null: nobody reads this link inside the chain)
-    int N, K, tiles, chunks;
+    int N, tiles, chunks;
+    int units_q, units_r;                       // tiles * chunks = grid * units_q + units_r: CTA b takes units_q (+1 if b < units_r)
     int src_tag;                                // tag offset of the producing link
     int tag;                                    // tag offset of this link
     int world;                                  // ranks the output is pushed to
     unsigned flags;
     float out_scale;
-    int pad[1];
 };
 static_assert(sizeof(ChainLinkDev) == 256, "link descriptor size");
 
@@ -198,7 +219,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 2000;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
@@ -288,23 +309,32 @@ __device__ float block_dot_fp32(const uint8_t *blk, const __half *x, const unsig
 
 // Units of a link that one warp of one CTA processes (units are numbered chunk-major).
 struct WarpRange {
-    int n_units, c_first, t_first;
+    int u_begin, n_units, c_first, t_first;
     int chunk_lo, chunk_hi;                 // chunks the CTA touches (chunk_hi < chunk_lo: none)
 };
-__device__ __forceinline__ WarpRange warp_range(int tiles, int chunks, int warp) {
+// u / tiles for 0 <= u < 2^22 and 1 <= tiles <= 2^16 without an integer division: the float quotient is off
+// by at most one, which the remainder corrects.
+__device__ __forceinline__ int div_tiles(int u, int tiles, float inv_tiles) {
+    int q = (int)((float)u * inv_tiles);
+    const int r = u - q * tiles;
+    q += r >= tiles ? 1 : 0;
+    q -= r < 0 ? 1 : 0;
+    return q;
+}
+__device__ __forceinline__ WarpRange warp_range(int tiles, int units_q, int units_r, int warp) {
     WarpRange r;
-    // tiles * chunks <= 2^22 and gridDim.x <= a few hundred, so the products fit 32 bits
-    const unsigned total = (unsigned)tiles * (unsigned)chunks;
-    const int cta_begin = (int)(total * blockIdx.x / gridDim.x);
-    const int cta_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
-    const int cta_units = cta_end - cta_begin;
-    const int u_begin = cta_begin + ((cta_units * warp) >> 4);
-    const int u_end = cta_begin + ((cta_units * (warp + 1)) >> 4);
-    r.n_units = u_end - u_begin;
-    r.chunk_lo = cta_units > 0 ? cta_begin / tiles : 0;
-    r.chunk_hi = cta_units > 0 ? (cta_end - 1) / tiles : -1;
-    r.c_first = u_begin / tiles;
-    r.t_first = u_begin - r.c_first * tiles;
+    const int b = (int)blockIdx.x;
+    const int cta_begin = b * units_q + min(b, units_r);
+    const int cta_units = units_q + (b < units_r ? 1 : 0);
+    const int cta_end = cta_begin + cta_units;
+    const float inv = __frcp_rn((float)tiles);
+    r.u_begin = cta_begin + (cta_units * warp) / kWarps;
+    const int u_end = cta_begin + (cta_units * (warp + 1)) / kWarps;
+    r.n_units = u_end - r.u_begin;
+    r.chunk_lo = cta_units > 0 ? div_tiles(cta_begin, tiles, inv) : 0;
+    r.chunk_hi = cta_units > 0 ? div_tiles(cta_end - 1, tiles, inv) : -1;
+    r.c_first = div_tiles(r.u_begin, tiles, inv);
+    r.t_first = r.u_begin - r.c_first * tiles;
     return r;
 }
 
@@ -353,7 +383,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
     const CUtensorMap *iss_map;
     auto cursor_load = [&]() {
         const ChainLinkDev &L = links[iss_link];
-        const WarpRange r = warp_range(L.tiles, L.chunks, warp);
+        const WarpRange r = warp_range(L.tiles, L.units_q, L.units_r, warp);
         iss_left = r.n_units; iss_c = r.c_first; iss_t = r.t_first; iss_tiles = L.tiles;
         iss_map = &L.wmap;
     };
@@ -364,7 +394,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             ++iss_link;
             cursor_load();
         }
-        const uint32_t s = (uint32_t)issued & (kStages - 1);
+        const uint32_t s = (uint32_t)issued % kStages;
         mbar_expect_tx(bar0 + 8u * s, kUnitBytes);
         tma_load_2d(ring_warp + s * kUnitBytes, iss_map, iss_c * kChunkBytes, iss_t * kTileRows, bar0 + 8u * s);
         ++issued;
@@ -408,6 +438,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
 
     bool dead = false;                                 // a bounded wait ran out: stop waiting, finish quickly
     __syncthreads();                                   // barriers initialised, planes zeroed
+    PHASE_DECL
 
     for (int p = 0; p < n_links; ++p) {
         const ChainLinkDev &L = links[p];
@@ -415,22 +446,27 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         const __half *xh = L.x;
         const unsigned long long *xin = L.xin;
         const unsigned flags = L.flags;
-        const WarpRange R = warp_range(tiles, chunks, warp);
+        const WarpRange R = warp_range(tiles, L.units_q, L.units_r, warp);
         const int n_units = R.n_units, chunk_lo = R.chunk_lo, chunk_hi = R.chunk_hi;
         const int buf = p & 1;
         uint32_t *btab = btab_all + buf * (kBtabOne / 4);
         float *red_max = reinterpret_cast<float *>(red_all + buf * kRedOne);       // [chunk][warp]
-        int *red_sum = reinterpret_cast<int *>(red_max + kMaxChunksPerCta * kWarps);
-        int *red_bad = red_sum + kMaxChunksPerCta * kWarps;
+        int *red_sum = reinterpret_cast<int *>(red_max + kMaxChunksPerCta * 16);
+        int *red_bad = red_sum + kMaxChunksPerCta * 16;
         const unsigned tag = tag_base + (unsigned)L.tag + 1u;
+        // Read the region's arrival counter now (checked after the first barrier below): its round trip then
+        // overlaps the wait for the activations instead of sitting between the two barriers.
+        unsigned arrived_early = 0u;
+        if (tid == 0 && p >= 2 && P.n_regions > 1) arrived_early = ctl_read(ctl + kCtlArrive + (p & 1));
 
         // ---- this CTA's activations: one thread per activation, which also fetches the activation
         // of the fifth trit of its code byte (needed for 81 x_i - 3^i x_4) -----------------------------
+        const bool prep = tid < kPrepThreads;
         float xv[kMaxChunksPerCta], x4v[kMaxChunksPerCta];
         if (xin == nullptr) {
 #pragma unroll
             for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
-                const bool live = chunk_lo + cl <= chunk_hi;
+                const bool live = prep && chunk_lo + cl <= chunk_hi;
                 const __half *xc = xh + (size_t)(chunk_lo + cl) * kChunkCols;
                 xv[cl] = live ? __half2float(xc[tid]) : 0.0f;
                 x4v[cl] = live ? __half2float(xc[fifth]) : 0.0f;
@@ -448,7 +484,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             unsigned long long wv[kMaxChunksPerCta], w4[kMaxChunksPerCta];
 #pragma unroll
             for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
-                const bool live = chunk_lo + cl <= chunk_hi;
+                const bool live = prep && chunk_lo + cl <= chunk_hi;
                 const unsigned long long *xc = xin + (size_t)(chunk_lo + cl) * kChunkCols;
                 wv[cl] = live ? word_read(xc + tid) : ((unsigned long long)want << 32);
                 w4[cl] = live ? word_read(xc + fifth) : ((unsigned long long)want << 32);
@@ -470,6 +506,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             }
         }
 
+        PHASE(0)
         // ---- activation digits: group maximum, fixed point, four signed byte planes --------------------
         bool bad[kMaxChunksPerCta];
         const int n_chunks_cta = chunk_hi - chunk_lo + 1;
@@ -485,7 +522,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
                 anybad |= __shfl_xor_sync(0xffffffffu, anybad, o);
             }
-            if (lane == 0) { red_max[cl * kWarps + warp] = m; red_bad[cl * kWarps + warp] = anybad; }
+            if (lane == 0 && prep) { red_max[cl * 16 + warp] = m; red_bad[cl * 16 + warp] = anybad; }
         }
         __syncthreads();
         // Every warp of this CTA has left link p-1, so the CTA is done with that link's slots; and
@@ -496,7 +533,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             if (p >= 2 && P.n_regions > 1) {
                 const unsigned need = gridDim.x * (unsigned)(p >> 1);
                 uint32_t spins = 0;
-                while (ctl_read(ctl + kCtlArrive + (p & 1)) < need) {
+                while (arrived_early < need && ctl_read(ctl + kCtlArrive + (p & 1)) < need) {
                     if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 6u); break; }
                 }
             }
@@ -504,12 +541,12 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         // every warp's first tile is on its way: now queue the rest of the ring behind them
         if (lane == 0)
             while (issued - consumed < kStages - 1 && issue_one()) {}
-        {
+        if (prep) {
             const int gw = warp & ~3;                          // the four warps of this thread's group
 #pragma unroll
             for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
                 if (cl >= n_chunks_cta) break;
-                const float *rm = red_max + cl * kWarps + gw;
+                const float *rm = red_max + cl * 16 + gw;
                 const float m = fmaxf(fmaxf(rm[0], rm[1]), fmaxf(rm[2], rm[3]));
                 // 2^E <= m < 2^(E+1); fixed point xi = round(v * 2^(21-E)), |xi| <= 2^22
                 const int e_biased = m > 0.0f ? (int)(__float_as_uint(m) >> 23) : 127;
@@ -518,7 +555,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                 int s = is_fifth ? 121 * xi : 0;                   // 121 * sum of the fifth-trit activations
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (lane == 0) red_sum[cl * kWarps + warp] = s;
+                if (lane == 0) red_sum[cl * 16 + warp] = s;
                 // value paired with this k-slot: x_4 for the raw byte, 81 x_i - 3^i x_4 for trit i < 4
                 int v = xi;
                 if (!is_fifth) {
@@ -541,6 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         }
         __syncthreads();
 
+        PHASE(1)
         if (p == 0) {                                   // the decode table must have landed
             uint32_t spins = 0;
             while (!mbar_try_wait(lut_bar, 0)) {
@@ -556,6 +594,8 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         int gbad[2];
         int cur_chunk = -1;
         int c = R.c_first, t = R.t_first;
+        // slot of row g of the current unit: units are numbered chunk-major, so it advances by 16 per unit
+        unsigned long long *mine = slots + (size_t)R.u_begin * kTileRows + g;
 
         for (int i = 0; i < n_units; ++i) {
             if (c != cur_chunk) {       // (re)load the B fragments and the group constants of this K chunk
@@ -566,7 +606,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
 #pragma unroll
                     for (int r = 0; r < kRegsPerSub; ++r)
                         breg[sub][r] = btab[((cl * 2 + sub) * kRegsPerSub + r) * 32 + lane];
-                    const int w4 = cl * kWarps + 4 * (sub + 2 * cls);          // the group's four warps
+                    const int w4 = cl * 16 + 4 * (sub + 2 * cls);              // the group's four warps
                     gsum[sub] = red_sum[w4] + red_sum[w4 + 1] + red_sum[w4 + 2] + red_sum[w4 + 3];
                     const float gm = fmaxf(fmaxf(red_max[w4], red_max[w4 + 1]), fmaxf(red_max[w4 + 2], red_max[w4 + 3]));
                     const int eb = gm > 0.0f ? (int)(__float_as_uint(gm) >> 23) : 127;
@@ -574,7 +614,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                     gbad[sub] = red_bad[w4] | red_bad[w4 + 1] | red_bad[w4 + 2] | red_bad[w4 + 3];
                 }
             }
-            const uint32_t s = (uint32_t)consumed & (kStages - 1);
+            const uint32_t s = (uint32_t)consumed % kStages;
             const uint32_t parity = ((uint32_t)consumed / kStages) & 1u;
             uint32_t arrived = 0;
             if (!dead) {
@@ -651,13 +691,14 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             acc1 += __shfl_down_sync(0xffffffffu, acc1, 2);
             acc2 += __shfl_down_sync(0xffffffffu, acc2, 2);
             if (q == 0) {       // value and tag travel in one 64-bit store, so whoever sees the tag has the value
-                unsigned long long *mine = slots + ((size_t)c * tiles + t) * kTileRows;
-                slot_publish(mine + g, acc1, tag);
-                slot_publish(mine + g + 8, acc2, tag);
+                slot_publish(mine, acc1, tag);
+                slot_publish(mine + 8, acc2, tag);
             }
+            mine += kTileRows;
             if (++t == tiles) { t = 0; ++c; }
         }
 
+        PHASE(2)
         // ---- finish row tiles ----------------------------------------------------------------------------
         // Row tile t is finished by a fixed owner, the warp that processed its chunk t % chunks. The
         // owner polls the tile's slots (bounded) until every chunk's value carries this link's tag. All
@@ -673,8 +714,9 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             void *y = L.y;
             const int world = L.world;
             int cc = R.c_first, tt = R.t_first;
+            int tm = R.t_first % chunks;                 // tt % chunks, kept up to date without dividing again
             for (int i = 0; i < n_units; ++i) {
-                if (tt % chunks == cc) {                 // warp-uniform: this warp owns row tile tt
+                if (tm == cc) {                          // warp-uniform: this warp owns row tile tt
                     const unsigned long long *ps = slots + (size_t)tt * kTileRows + r;
                     float total = 0.0f;
                     for (int c0 = hf; c0 < chunks; c0 += 16) {
@@ -717,10 +759,13 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                             word_publish(L.xout[pr] + row, (uint32_t)__half_as_ushort(hv), tag);
                     }
                 }
-                if (++tt == tiles) { tt = 0; ++cc; }
+                if (++tm == chunks) tm = 0;
+                if (++tt == tiles) { tt = 0; tm = 0; ++cc; }
             }
         }
+        PHASE(3)
     }
+    PHASE_DUMP
 
     // ---- leave: the last CTA resets the launch-scoped counters and moves the tag base on ----------------
     __syncthreads();
@@ -785,10 +830,10 @@ int device_state(DeviceState **out) {
 // A CTA keeps the digit planes of at most kMaxChunksPerCta chunks: check that no CTA of a grid of
 // `grid` CTAs spans more.
 bool span_ok(int tiles, int chunks, int grid) {
-    const unsigned total = (unsigned)tiles * (unsigned)chunks;
+    const int total = tiles * chunks, q = total / grid, r = total % grid;
     for (int b = 0; b < grid; ++b) {
-        const int begin = (int)(total * (unsigned)b / (unsigned)grid);
-        const int end = (int)(total * (unsigned)(b + 1) / (unsigned)grid);
+        const int begin = b * q + (b < r ? b : r);
+        const int end = begin + q + (b < r ? 1 : 0);
         if (end > begin && (end - 1) / tiles - begin / tiles + 1 > kMaxChunksPerCta) return false;
     }
     return true;
@@ -919,9 +964,10 @@ int gemv_chain_describe(const tq1_chain_link *links, int n_links, int rank, int 
                 d.y = l.y_is_f32 ? static_cast<void *>(static_cast<float *>(l.y) + out0)
                                  : static_cast<void *>(static_cast<__half *>(l.y) + out0);
             d.N = rows;
-            d.K = l.K;
             d.tiles = (rows + kTileRows - 1) / kTileRows;
             d.chunks = l.K / kChunkCols;
+            d.units_q = d.tiles * d.chunks / grid;
+            d.units_r = d.tiles * d.chunks % grid;
             if (!span_ok(d.tiles, d.chunks, grid))
                 return fail(TQ1_ERR_INVALID, "tq1 chain: link %d (%dx%d) spreads a CTA over more than %d K chunks",
                             i, l.N, l.K, kMaxChunksPerCta);
@@ -1091,6 +1137,12 @@ int gemv_noalloc_status(unsigned *out_host, cudaStream_t stream) {
 }
 
 }  // namespace tq1
+
+#ifdef TQ1_PHASE_TIMERS
+extern "C" int tq1_debug_read_phases(long long *out, int count) {
+    return (int)cudaMemcpyFromSymbol(out, tq1::g_phase_acc, sizeof(long long) * count);
+}
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // C ABI of the chain (declared in include/ternel_b200.h).
