@@ -1,23 +1,33 @@
 """A stack of packed decoder-layer projections resident on one GPU.
 
 This is the decode-step harness used by the benchmark and the multi-GPU tests:
-``layers`` copies of the seven projections of a dense decoder layer (q, k, v,
-o, gate, up, down), each a ``PackedLinear``-shaped weight of canonical blocks,
-optionally output-row-sharded over the ranks of a process group. One ``step``
-streams every weight byte once (the batch-1 / small-batch regime of
+``layers`` copies of the projections of a dense decoder layer (q, k, v, o, gate,
+up, down), each a ``PackedLinear``-shaped weight of canonical blocks, optionally
+output-row-sharded over the ranks of a process group. One ``step`` streams every
+weight byte once (the batch-1 / small-batch regime of
 src/ternel_mlx/modules.py:425-457 of the reference, where a decoded token issues
-one matmul per linear leaf), gathers one embedding row per sequence, and, when
-sharded, all-gathers each projection's output shards so every rank holds the
-whole activation again.
+one matmul per linear leaf) and gathers one embedding row per sequence.
 
-Inputs of the projections are fixed synthetic activations (no attention or
-normalisation sits between them here), so the values stay finite while the
-launch order and the bytes moved are those of a real decode step.
+Exchange modes:
+
+* ``"chain"`` (batch 1): the whole step is ONE persistent launch
+  (``ternel_b200.chain.ChainPlan``). Projections depend on each other the way a
+  decoder's do: q|k|v reads the previous layer's output (the embedding row for the
+  first layer), o reads the q part of q|k|v, gate|up reads o and applies
+  ``silu(gate) * up`` in its epilogue, down reads that. No attention or
+  normalisation sits in between, so every link carries an output scale that keeps
+  the activations at unit scale through all layers. With several ranks every
+  finished output is pushed into every rank's hand-off area by the kernel itself
+  (symmetric memory, plain peer stores).
+* ``"launches"``: one launch per projection over fixed synthetic inputs (any
+  batch); with several ranks the shards are all-gathered by NCCL after each
+  projection (the baseline exchange).
 """
 
 from __future__ import annotations
 
 import ctypes
+import math
 from dataclasses import dataclass
 
 import torch
@@ -78,12 +88,29 @@ def random_blocks_device(rows: int, columns: int, generator: torch.Generator, de
     return out.reshape(rows, columns // BLOCK_SIZE, BLOCK_BYTES)
 
 
+def unit_gain(columns: int, p_zero: float = 0.40, scale_second_moment: float = 0.02 ** 2) -> float:
+    """Output scale that keeps a unit-RMS activation vector at unit RMS through a random packed linear:
+    the output variance is ``columns * P(nonzero) * E[scale^2]`` times the input's."""
+    return 1.0 / math.sqrt(columns * (1.0 - p_zero) * scale_second_moment)
+
+
+def swiglu_gain(pre_rms: float) -> float:
+    """1 / RMS of ``silu(g) * u`` for independent ``g, u ~ N(0, pre_rms^2)`` (fixed-seed Monte Carlo, so
+    that every rank computes the same number)."""
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(1234)
+    g = torch.randn(1 << 20, generator=gen, dtype=torch.float64) * pre_rms
+    u = torch.randn(1 << 20, generator=gen, dtype=torch.float64) * pre_rms
+    return 1.0 / float(((g / (1 + torch.exp(-g)) * u) ** 2).mean().sqrt())
+
+
 class LayerStack:
-    """``layers`` x 7 packed projections (+ an embedding table), row-sharded over ``world`` ranks."""
+    """``layers`` x the projections of a decoder layer (+ an embedding table), row-sharded over ``world`` ranks."""
 
     def __init__(self, *, layers: int, batch: int = 1, shape: LayerShape = LayerShape(),
                  vocab: int = 0, rank: int = 0, world: int = 1, device=None, seed: int = 0,
-                 group=None, fused: bool = False, exchange: str = "p2p", weights_from: "LayerStack | None" = None) -> None:
+                 group=None, fused: bool = False, exchange: str = "chain", dependent: bool = True,
+                 weights_from: "LayerStack | None" = None) -> None:
         self.layers, self.batch, self.shape = layers, batch, shape
         self.rank, self.world, self.group = rank, world, group
         self.device = torch.device(device if device is not None else "cuda")
@@ -93,8 +120,14 @@ class LayerStack:
         self.fused = fused
         self.projections = shape.projections(fused)
         for _, n, _ in self.projections:
-            if n % world or (n // world) % 16:
+            if n % world or (n // world) % 32:
                 raise ValueError(f"{n} output rows do not shard evenly over {world} ranks")
+        if exchange not in ("chain", "launches"):
+            raise ValueError(f"unknown exchange mode {exchange!r}")
+        if exchange == "chain" and batch != 1:
+            raise ValueError("the chain runs batch 1; use exchange='launches' for larger batches")
+        self.exchange = exchange
+        self.dependent = dependent and exchange == "chain"
         # weights[l][j]: this rank's rows [rank*N/P, (rank+1)*N/P) of projection j in layer l
         if weights_from is not None:       # a second stack (another batch size) over the same resident weights
             if (weights_from.projections, weights_from.world, weights_from.layers) != (self.projections, world, layers):
@@ -107,55 +140,133 @@ class LayerStack:
         xg.manual_seed(seed + 7)   # same activations on every rank
         self.inputs = {k: torch.randn((batch, k), generator=xg, device=self.device).to(torch.float16)
                        for k in sorted({k for _, _, k in self.projections})}
-        # full-width outputs; a rank computes its slice [.., rank*N/P:(rank+1)*N/P] and gathers the rest
-        self.shards = {n: torch.zeros((batch, n // world), dtype=torch.float16, device=self.device)
-                       for n in sorted({n for _, n, _ in self.projections})}
-        self.outputs = {n: torch.zeros((world, batch, n // world), dtype=torch.float16, device=self.device)
-                        for n in sorted({n for _, n, _ in self.projections})}
         self.vocab = vocab
         if vocab:
+            tg = torch.Generator(device=self.device)
+            tg.manual_seed(seed * 1000 + 999)          # the table is replicated: same bytes on every rank
             self.table = (weights_from.table if weights_from is not None and weights_from.vocab == vocab
-                          else random_blocks_device(vocab, shape.hidden, gen, self.device))
+                          else random_blocks_device(vocab, shape.hidden, tg, self.device))
             self.ids = torch.randint(0, vocab, (batch,), generator=xg, device=self.device)
             self.embedded = torch.zeros((batch, shape.hidden), dtype=torch.float16, device=self.device)
-        ws_bytes = max(self.lib.tq1_linear_workspace_bytes(batch, n // world, k) for _, n, k in self.projections)
-        self.workspace = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=self.device)
-        self.workspace_bytes = ws_bytes
-        self.launches_per_step = layers * len(self.projections) + (1 if vocab else 0)
-        self.exchange = exchange if world > 1 else "none"
-        if self.exchange == "p2p":
-            self._setup_peer_buffers()
+        self.launches_per_step = (1 if exchange == "chain" else layers * len(self.projections)) + (1 if vocab else 0)
+        self.links_per_step = layers * len(self.projections)
+        if exchange == "chain":
+            self._setup_chain()
+        else:
+            # full-width outputs; a rank computes its slice and NCCL gathers the rest
+            sizes = sorted({n for _, n, _ in self.projections})
+            self.shards = {n: torch.zeros((batch, n // world), dtype=torch.float16, device=self.device) for n in sizes}
+            self.outputs = {n: torch.zeros((world, batch, n // world) if world > 1 else (batch, n), dtype=torch.float16,
+                                           device=self.device) for n in sizes}
+            ws_bytes = max(self.lib.tq1_linear_workspace_bytes(batch, n // world, k) for _, n, k in self.projections)
+            self.workspace = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=self.device)
+            self.workspace_bytes = ws_bytes
 
-    def _setup_peer_buffers(self) -> None:
-        """Gathered outputs and flags in symmetric memory so every rank can write into every other's."""
+    # ------------------------------------------------------------------
+    def chain_links(self, layers: "int | None" = None):
+        """The step as chain links over this rank's weight shards (see the module docstring)."""
+        from .chain import Link
+        shape, world = self.shape, self.world
+        hidden = shape.hidden
+        links, outs = [], []
+        q_rows = shape.q_heads * shape.head_dim
+        # the first layer reads the gathered embedding row; its output scale also brings that row to unit RMS
+        x0 = self.embedded[0] if self.vocab else self.inputs[hidden][0]
+        x0_gain = self.embedding_gain if self.vocab else 1.0
+        for layer in range(self.layers if layers is None else layers):
+            blocks = self.weights[layer]
+            base = len(links)
+            for j, (name, n, k) in enumerate(self.projections):
+                swiglu = self.dependent and name == "gate_up"
+                n_out = (n // 2 if swiglu else n) // world
+                y = torch.zeros(n_out, dtype=torch.float16, device=self.device)
+                link = Link(blocks=blocks[j], y=y, swiglu=swiglu)
+                if not self.dependent:
+                    link.x = self.inputs[k][0]
+                    link.out_scale = unit_gain(k)
+                elif name in ("qkv", "q", "k", "v"):
+                    link.out_scale = unit_gain(k)
+                    if layer == 0:
+                        link.x = x0
+                        link.out_scale *= x0_gain
+                    else:
+                        link.source = base - 1                      # the previous layer's down projection
+                elif name == "o":
+                    link.source, link.source_offset = base, 0       # the q part of q|k|v (or q itself)
+                    link.out_scale = unit_gain(k)
+                    assert q_rows == k
+                elif name in ("gate_up", "gate", "up"):
+                    link.source = base + (1 if self.fused else 3)   # the o projection
+                    link.out_scale = swiglu_gain(1.0 / unit_gain(k)) if swiglu else unit_gain(k)
+                elif name == "down":
+                    if self.fused:
+                        link.source = base + 2                      # silu(gate) * up
+                    else:
+                        link.x = self.inputs[k][0]                  # separate gate and up matrices cannot be fused here
+                    link.out_scale = unit_gain(k)
+                links.append(link)
+                outs.append(y)
+        return links, outs
+
+    def _calibrate(self, links) -> None:
+        """Measured output scales: every link is run once, in order, through the plain entry point on this rank's
+        rows, and its scale is set so that the gathered output has unit RMS (the sums of squares are all-reduced,
+        so every rank arrives at the same numbers). The analytic gains drift by a fraction of a percent per link,
+        which over hundreds of dependent links leaves the FP16 range."""
         import torch.distributed as dist
-        import torch.distributed._symmetric_memory as symm_mem
-        from .sharding import EpochClock, ShardPlan
-
-        sizes = sorted({n for _, n, _ in self.projections})
-        # arena: [epoch base 4 B | pad to 1 KiB] then, per output size, the gathered buffer and its tile flags
-        self._offsets, self._flag_offsets, cursor = {}, {}, 1024
-        for n in sizes:
-            self._offsets[n] = cursor
-            cursor += (self.batch * n * 2 + 255) // 256 * 256
-            self._flag_offsets[n] = cursor
-            cursor += (n // 16 * 4 + 255) // 256 * 256
-        arena = symm_mem.empty(cursor, dtype=torch.uint8, device=self.device)
-        arena.zero_()
-        handle = symm_mem.rendezvous(arena, self.group if self.group is not None else dist.group.WORLD)
-        self._arena, self._handle = arena, handle
-        self._peer_base = [int(p) for p in handle.buffer_ptrs]
-        self.outputs = {n: arena[self._offsets[n]: self._offsets[n] + self.batch * n * 2].view(torch.float16)
-                        .view(self.batch, n) for n in sizes}
-        self._plans = {n: ShardPlan(n, self.world) for n in sizes}
-        self._clock = EpochClock()
-        self._epoch_base_ptr = self._peer_base[self.rank]
-        ws_bytes = max(self.lib.tq1_linear_sharded_workspace_bytes(self.batch, n // self.world, k)
-                       for _, n, k in self.projections)
-        self.workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device=self.device)
-        self.workspace_bytes = ws_bytes
+        from .ops import tq1_matmul
+        if self.vocab:          # the gathered row the first link reads
+            check(self.lib.tq1_embedding_f16(self.table.data_ptr(), self.ids.data_ptr(), self.embedded.data_ptr(), 0,
+                                             self.batch, self.vocab, self.shape.hidden,
+                                             ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)))
+        gathered = {}
+        for i, link in enumerate(links):
+            if link.x is not None:
+                x = link.x
+            else:
+                x = gathered[link.source][link.source_offset: link.source_offset + link.columns]
+            y = tq1_matmul(link.blocks, x.reshape(1, -1).contiguous(), out_dtype=torch.float32)[0]
+            if link.swiglu:
+                gate, up = y[0::2], y[1::2]
+                y = gate / (1.0 + torch.exp(-gate)) * up
+            stats = torch.stack((y.double().pow(2).sum(), torch.tensor(float(y.numel()), dtype=torch.float64, device=y.device)))
+            if self.world > 1:
+                dist.all_reduce(stats, group=self.group)
+            rms = math.sqrt(float(stats[0] / stats[1]))
+            link.out_scale = 1.0 / max(rms, 1e-20)
+            out = (y * link.out_scale).to(torch.float16)
+            if self.world > 1:
+                full = torch.empty((self.world, out.numel()), dtype=out.dtype, device=out.device)
+                dist.all_gather_into_tensor(full, out.contiguous(), group=self.group)
+                out = full.reshape(-1)
+            gathered[i] = out
+            for j in [j for j in gathered if j < i - 8]:        # sources are never more than a layer back
+                del gathered[j]
         torch.cuda.synchronize(self.device)
-        dist.barrier(group=self.group)
+
+    def _setup_chain(self) -> None:
+        from .chain import ChainPlan
+        self.embedding_gain = 1.0 / math.sqrt(0.6 * 0.02 ** 2)      # a decoded embedding row has RMS sqrt(0.6) * 0.02
+        links, self.link_outputs = self.chain_links()
+        if self.dependent:
+            self._calibrate(links)
+        peers = None
+        if self.world > 1:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+            from .chain import _pack_links
+            nbytes = self.lib.tq1_chain_handoff_bytes(_pack_links(links), len(links), self.world)
+            area = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+            area.zero_()
+            handle = symm_mem.rendezvous(area, self.group if self.group is not None else dist.group.WORLD)
+            self._handoff, self._handle = area, handle
+            peers = (self.rank, self.world, [int(p) for p in handle.buffer_ptrs])
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
+        self.plan = ChainPlan(links, peers=peers)
+        self.workspace = self.plan.workspace
+        self.workspace_bytes = self.workspace.numel()
+        torch.cuda.synchronize(self.device)
 
     # ------------------------------------------------------------------
     @property
@@ -178,13 +289,13 @@ class LayerStack:
         """Enqueue one decode step on the current stream (no synchronisation)."""
         stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         lib, batch, world = self.lib, self.batch, self.world
-        ws, ws_bytes = self.workspace.data_ptr(), self.workspace_bytes
         if self.vocab:
             check(lib.tq1_embedding_f16(self.table.data_ptr(), self.ids.data_ptr(), self.embedded.data_ptr(),
                                         0, batch, self.vocab, self.shape.hidden, stream))
-        if self.exchange == "p2p":
-            self._step_p2p(stream)
+        if self.exchange == "chain":
+            self.plan.run()
             return
+        ws, ws_bytes = self.workspace.data_ptr(), self.workspace_bytes
         for layer in self.weights:
             for (_, n, k), blocks in zip(self.projections, layer):
                 if world == 1:
@@ -197,28 +308,13 @@ class LayerStack:
                                              batch, n // world, k, ws, ws_bytes, stream))
                     torch.distributed.all_gather_into_tensor(self.outputs[n], shard, group=self.group)
 
-    def _step_p2p(self, stream) -> None:
-        """Every projection pushes its rows into all ranks' gathered buffers; the next one waits for the flags."""
-        from .sharding import make_shard, sharded_linear
-        lib, world, rank = self.lib, self.world, self.rank
-        local = self._peer_base[rank]
-        prev_n = self.projections[-1][1]          # a step starts after the previous step's last projection
-        for layer in self.weights:
-            for (_, n, k), blocks in zip(self.projections, layer):
-                publish, wait = self._clock.next()
-                # the input stands for the previous projection's gathered output: wait for the tiles of
-                # that buffer which cover this projection's K columns
-                shard = make_shard(rank=rank, plan=self._plans[n],
-                                   peer_y=[base + self._offsets[n] for base in self._peer_base],
-                                   peer_flags=[base + self._flag_offsets[n] for base in self._peer_base],
-                                   epoch_base=self._epoch_base_ptr, publish_epoch=publish, wait_epoch=wait,
-                                   wait_flags=local + self._flag_offsets[prev_n], wait_tiles=min(k, prev_n) // 16)
-                sharded_linear(lib, blocks.data_ptr(), self.inputs[k].data_ptr(), shard, batch=self.batch,
-                               n_local=n // world, columns=k, workspace_ptr=self.workspace.data_ptr(),
-                               workspace_bytes=self.workspace_bytes, stream_ptr=stream)
-                prev_n = n
-        check(lib.tq1_shard_advance_epoch(self._epoch_base_ptr, self._clock.reset(), stream))
+    def status(self) -> int:
+        """Word 0 of the workspace: non-zero after a bounded device wait ran out (synchronises)."""
+        return int(self.workspace[:4].view(torch.int32)[0].item())
 
     def checksum(self) -> float:
-        """Consumes every output so the work cannot be dead-coded; also a cross-rank equality check."""
+        """Consumes the outputs so the work cannot be dead-coded. In chain mode the last link's output depends on
+        every earlier link of every rank."""
+        if self.exchange == "chain":
+            return float(sum(y.float().abs().sum() for y in self.link_outputs[-len(self.projections):]))
         return float(sum(v.float().abs().sum() for v in self.outputs.values()))
