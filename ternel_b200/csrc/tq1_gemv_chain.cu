@@ -41,8 +41,7 @@
 // Shared-memory traffic sets the pace of the loop (one 128-byte wavefront per 32 code bytes
 // for the table alone), so the loop spends as few load/store-pipe operations as it can:
 // plane pairs are combined before they are exchanged (two shuffles per 16 rows x 2 groups
-// instead of four), slots are never cleared, and the digit planes are written without bank
-// conflicts.
+// instead of four) and slots are never cleared.
 #include <cuda.h>
 #include <stdlib.h>
 #include <string.h>
@@ -87,7 +86,8 @@ constexpr uint32_t kBtabBytes = 2 * kBtabOne;                                   
 constexpr uint32_t kMbarBytes = 8 * (kWarps * kStages + 2);
 constexpr uint32_t kRedOne = 3 * 4 * 16 * kMaxChunksPerCta;                        // group max / sum / non-finite
 constexpr uint32_t kRedBytes = 2 * kRedOne;
-constexpr uint32_t kHighBytes = kBtabBytes + kMbarBytes + kRedBytes;
+constexpr uint32_t kXsBytes = kMaxChunksPerCta * kChunkCols * 4;                    // the CTA's activations as FP32
+constexpr uint32_t kHighBytes = kBtabBytes + kMbarBytes + kRedBytes + kXsBytes;
 static_assert(kRingBytes + 1024 + 128 <= kLutWindowAddr, "the ring must end below the table's fixed address");
 static_assert(kWindowEnd + kHighBytes <= 227 * 1024, "shared memory budget");
 constexpr uint32_t kMaxWaitSpins = 1u << 21;
@@ -346,6 +346,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
     uint32_t *btab_all = reinterpret_cast<uint32_t *>(high);
     uint64_t *mbars = reinterpret_cast<uint64_t *>(high + kBtabBytes);
     unsigned char *red_all = high + kBtabBytes + kMbarBytes;
+    float *xs = reinterpret_cast<float *>(high + kBtabBytes + kMbarBytes + kRedBytes);   // [chunk][activation]
     unsigned *ctl = P.ctl;
     if (window + kRingBytes > kLutWindowAddr) {      // the fixed-address table would overlap the ring
         if (threadIdx.x == 0) atomicExch(ctl + kCtlStatus, 2u);
@@ -462,14 +463,13 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         // ---- this CTA's activations: one thread per activation, which also fetches the activation
         // of the fifth trit of its code byte (needed for 81 x_i - 3^i x_4) -----------------------------
         const bool prep = tid < kPrepThreads;
-        float xv[kMaxChunksPerCta], x4v[kMaxChunksPerCta];
+        float xv[kMaxChunksPerCta];
         if (xin == nullptr) {
 #pragma unroll
             for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
                 const bool live = prep && chunk_lo + cl <= chunk_hi;
                 const __half *xc = xh + (size_t)(chunk_lo + cl) * kChunkCols;
                 xv[cl] = live ? __half2float(xc[tid]) : 0.0f;
-                x4v[cl] = live ? __half2float(xc[fifth]) : 0.0f;
             }
             // The activation loads are in flight: now start this warp's weight tiles (issued the other
             // way round the few activation bytes queue behind megabytes of weight traffic). One tile
@@ -481,13 +481,12 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             if (lane == 0)
                 while (issued - consumed < kStages - 1 && issue_one()) {}
             const unsigned want = tag_base + (unsigned)L.src_tag + 1u;
-            unsigned long long wv[kMaxChunksPerCta], w4[kMaxChunksPerCta];
+            unsigned long long wv[kMaxChunksPerCta];
 #pragma unroll
             for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
                 const bool live = prep && chunk_lo + cl <= chunk_hi;
                 const unsigned long long *xc = xin + (size_t)(chunk_lo + cl) * kChunkCols;
                 wv[cl] = live ? word_read(xc + tid) : ((unsigned long long)want << 32);
-                w4[cl] = live ? word_read(xc + fifth) : ((unsigned long long)want << 32);
             }
 #pragma unroll
             for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
@@ -497,12 +496,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                     if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 4u); dead = true; break; }
                     wv[cl] = word_read(xc + tid);
                 }
-                while ((unsigned)(w4[cl] >> 32) != want && !dead) {
-                    if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 4u); dead = true; break; }
-                    w4[cl] = word_read(xc + fifth);
-                }
                 xv[cl] = __half2float(__ushort_as_half((unsigned short)(wv[cl] & 0xffffu)));
-                x4v[cl] = __half2float(__ushort_as_half((unsigned short)(w4[cl] & 0xffffu)));
             }
         }
 
@@ -510,21 +504,21 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         // ---- activation digits: group maximum, fixed point, four signed byte planes --------------------
         bool bad[kMaxChunksPerCta];
         const int n_chunks_cta = chunk_hi - chunk_lo + 1;
+        if (prep) {
 #pragma unroll
-        for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
-            if (cl >= n_chunks_cta) break;
-            const float a = fabsf(xv[cl]);
-            bad[cl] = !(a <= 65504.0f);                        // NaN or Inf
-            float m = bad[cl] ? 0.0f : a;
-            int anybad = bad[cl];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                anybad |= __shfl_xor_sync(0xffffffffu, anybad, o);
+            for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
+                if (cl >= n_chunks_cta) break;
+                const float a = fabsf(xv[cl]);
+                bad[cl] = !(a <= 65504.0f);                        // NaN or Inf
+                // non-negative floats order like their bit patterns: one redux instruction per warp
+                const unsigned m = __reduce_max_sync(0xffffffffu, bad[cl] ? 0u : __float_as_uint(a));
+                const int anybad = __any_sync(0xffffffffu, bad[cl]);
+                xs[cl * kChunkCols + tid] = xv[cl];                // the threads of a code byte's first four trits need its fifth
+                if (lane == 0) { red_max[cl * 16 + warp] = __uint_as_float(m); red_bad[cl * 16 + warp] = anybad; }
             }
-            if (lane == 0 && prep) { red_max[cl * 16 + warp] = m; red_bad[cl * 16 + warp] = anybad; }
         }
         __syncthreads();
+        PHASE(4)
         // Every warp of this CTA has left link p-1, so the CTA is done with that link's slots; and
         // before anybody publishes into the region link p shares with link p-2, every CTA must be
         // done with link p-2's slots.
@@ -541,41 +535,38 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         // every warp's first tile is on its way: now queue the rest of the ring behind them
         if (lane == 0)
             while (issued - consumed < kStages - 1 && issue_one()) {}
+        PHASE(5)
         if (prep) {
             const int gw = warp & ~3;                          // the four warps of this thread's group
 #pragma unroll
             for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
                 if (cl >= n_chunks_cta) break;
-                const float *rm = red_max + cl * 16 + gw;
-                const float m = fmaxf(fmaxf(rm[0], rm[1]), fmaxf(rm[2], rm[3]));
+                const float4 rm = *reinterpret_cast<const float4 *>(red_max + cl * 16 + gw);
+                const float m = fmaxf(fmaxf(rm.x, rm.y), fmaxf(rm.z, rm.w));
                 // 2^E <= m < 2^(E+1); fixed point xi = round(v * 2^(21-E)), |xi| <= 2^22
                 const int e_biased = m > 0.0f ? (int)(__float_as_uint(m) >> 23) : 127;
                 const float up = __uint_as_float((uint32_t)(275 - e_biased) << 23);            // 2^(21-E)
                 const int xi = bad[cl] ? 0 : __float2int_rn(xv[cl] * up);
-                int s = is_fifth ? 121 * xi : 0;                   // 121 * sum of the fifth-trit activations
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                // 121 * sum of the fifth-trit activations of this warp's 32 activations
+                const int s = __reduce_add_sync(0xffffffffu, is_fifth ? 121 * xi : 0);
                 if (lane == 0) red_sum[cl * 16 + warp] = s;
                 // value paired with this k-slot: x_4 for the raw byte, 81 x_i - 3^i x_4 for trit i < 4
                 int v = xi;
                 if (!is_fifth) {
-                    const float a4 = fabsf(x4v[cl]);
-                    const int x4 = (el < 125 && a4 <= 65504.0f) ? __float2int_rn(x4v[cl] * up) : 0;
+                    const float x4f = xs[cl * kChunkCols + fifth];
+                    const int x4 = (el < 125 && fabsf(x4f) <= 65504.0f) ? __float2int_rn(x4f * up) : 0;
                     v = 81 * xi - pow3 * x4;
                 }
-                const int d0 = (v << 24) >> 24;
-                const int r1 = (v - d0) >> 8;
-                const int d1 = (r1 << 24) >> 24;
-                const int r2 = (r1 - d1) >> 8;
-                const int d2 = (r2 << 24) >> 24;
-                const int d3 = (r2 - d2) >> 8;
+                // four signed byte digits: the bytes of v + 0x80808080 are the digits plus 128
+                const uint32_t d = ((uint32_t)v + 0x80808080u) ^ 0x80808080u;
                 unsigned char *base = reinterpret_cast<unsigned char *>(btab) + cl * (2 * kRegsPerSub * 32 * 4) + plane_off;
-                base[0] = (unsigned char)d0;
-                base[16] = (unsigned char)d1;
-                base[32] = (unsigned char)d2;
-                base[48] = (unsigned char)d3;
+                base[0] = (unsigned char)d;
+                base[16] = (unsigned char)(d >> 8);
+                base[32] = (unsigned char)(d >> 16);
+                base[48] = (unsigned char)(d >> 24);
             }
         }
+        PHASE(6)
         __syncthreads();
 
         PHASE(1)
