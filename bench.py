@@ -278,7 +278,8 @@ def verify_chain(stack, world: int, rank: int) -> dict:
             x = link.x.float().cpu().numpy()
         else:
             x = full_out[link.source][link.source_offset: link.source_offset + k]
-        want = c_oracle.matmul_f32(link.blocks.cpu().numpy(), x[None, :].astype(np.float32), rows=link.rows, columns=k)[0]
+        canonical = stack.weights[i // per_layer][i % per_layer]      # the link may stream a permuted copy of these bytes
+        want = c_oracle.matmul_f32(canonical.cpu().numpy(), x[None, :].astype(np.float32), rows=link.rows, columns=k)[0]
         if link.swiglu:
             gate, up = want[0::2], want[1::2]
             want = gate / (1.0 + np.exp(-gate)) * up
@@ -516,14 +517,14 @@ def graph_time_us(device, run, replays: int, launches: int) -> float:
 
 def measure_shapes(device, ring: int = 64, replays: int = 8):
     """Batch-1 product per configured shape (the seven projection shapes, the two fused ones and 4096x4096):
-    * stream: `ring` distinct weight buffers (far more than L2 in total, except the smallest shapes, whose ring
+    * stream: `ring` distinct weight buffers in the chunk-major panel layout (far more than L2 in total, except the smallest shapes, whose ring
       is enlarged to exceed twice L2) as independent links of one chain launch -- the HBM number;
     * warm: the same buffer `ring` times in one chain launch -- L2-resident weights;
     * launches: `ring` separate launches of the plain entry point over the distinct buffers (stream order)."""
     import ctypes
     import torch
     from ternel_b200 import _native
-    from ternel_b200.chain import ChainPlan, Link
+    from ternel_b200.chain import ChainPlan, Link, blocks_to_panels
     from ternel_b200.format import check
     from ternel_b200.stack import random_blocks_device
 
@@ -542,8 +543,10 @@ def measure_shapes(device, ring: int = 64, replays: int = 8):
         y = torch.empty(n, dtype=torch.float16, device=device)
         ws = torch.zeros(lib.tq1_linear_workspace_bytes(1, n, k), dtype=torch.uint8, device=device)
         alg = bytes_one + 2 * (n + k)
-        stream_plan = ChainPlan([Link(blocks=w, x=x, y=y) for w in weights])
-        warm_plan = ChainPlan([Link(blocks=weights[0], x=x, y=y) for _ in weights], workspace=stream_plan.workspace)
+        panels = [blocks_to_panels(w) for w in weights]
+        stream_plan = ChainPlan([Link(blocks=w, panel_rows=n, x=x, y=y) for w in panels])
+        warm_plan = ChainPlan([Link(blocks=panels[0], panel_rows=n, x=x, y=y) for _ in panels], workspace=stream_plan.workspace)
+        canon_plan = ChainPlan([Link(blocks=w, x=x, y=y) for w in weights], workspace=stream_plan.workspace)
 
         def launches():
             stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
@@ -553,20 +556,22 @@ def measure_shapes(device, ring: int = 64, replays: int = 8):
 
         us_stream = graph_time_us(device, stream_plan.run, replays, count)
         us_warm = graph_time_us(device, warm_plan.run, replays, count)
+        us_canon = graph_time_us(device, canon_plan.run, replays, count)
         us_launch = graph_time_us(device, launches, replays, count)
         assert stream_plan.status() == 0
         out[f"{n}x{k}"] = {"stream_us": us_stream, "stream_gbps": alg / us_stream / 1e3,
                            "warm_l2_us": us_warm, "warm_l2_gbps": alg / us_warm / 1e3,
+                           "canonical_layout_stream_us": us_canon, "canonical_layout_stream_gbps": alg / us_canon / 1e3,
                            "separate_launch_us": us_launch, "separate_launch_gbps": alg / us_launch / 1e3,
                            "ring_buffers": count, "algorithmic_bytes": alg}
-        stream_plan.close(); warm_plan.close()
-        del weights, stream_plan, warm_plan
+        stream_plan.close(); warm_plan.close(); canon_plan.close()
+        del weights, panels, stream_plan, warm_plan, canon_plan
     # sensitivity: the converted model's measured trit frequencies (35.2% / 29.7% / 35.1%)
     n, k = 34816, 5120
-    weights = [random_blocks_device(n, k, gen, device, p_zero=0.297) for _ in range(16)]
+    weights = [blocks_to_panels(random_blocks_device(n, k, gen, device, p_zero=0.297)) for _ in range(16)]
     x = torch.randn(k, generator=gen, device=device).to(torch.float16)
     y = torch.empty(n, dtype=torch.float16, device=device)
-    plan = ChainPlan([Link(blocks=w, x=x, y=y) for w in weights])
+    plan = ChainPlan([Link(blocks=w, panel_rows=n, x=x, y=y) for w in weights])
     us = graph_time_us(device, plan.run, replays, len(weights))
     out["sensitivity_real_trit_frequencies_34816x5120"] = {
         "stream_us": us, "stream_gbps": (n * k // 128 * 28 + 2 * (n + k)) / us / 1e3, "p_zero": 0.297, "ring_buffers": len(weights)}
@@ -585,10 +590,17 @@ def measure_step_variants(args, stack, device, replays: int = 10):
     out = {}
     links, _ = stack.chain_links()
     scratch = {n: torch.empty(n, dtype=torch.float16, device=device) for n in {l.rows for l in links}}
-    independent = [Link(blocks=l.blocks, x=stack.inputs[l.columns][0], y=scratch[l.rows], out_scale=1.0) for l in links]
+    independent = [Link(blocks=l.blocks, panel_rows=l.panel_rows, x=stack.inputs[l.columns][0], y=scratch[l.rows],
+                        out_scale=1.0) for l in links]
     plan = ChainPlan(independent)
     out["chain_independent_links_ms"] = graph_time_us(device, plan.run, replays, 1) / 1e3
     plan.close()
+    if stack.use_panels:        # the same dependent step streaming the canonical blocks (strided 112-byte rows)
+        canon, _ = stack.chain_links(panels=False)
+        plan = ChainPlan(canon)
+        out["chain_canonical_layout_ms"] = graph_time_us(device, plan.run, replays, 1) / 1e3
+        plan.close()
+    links, _ = stack.chain_links(panels=False)
     lib = stack.lib
     ws = torch.zeros(max(lib.tq1_linear_workspace_bytes(1, l.rows, l.columns) for l in links), dtype=torch.uint8, device=device)
     outs = {n: torch.empty(n, dtype=torch.float16, device=device) for n in {l.rows for l in links}}

@@ -135,10 +135,6 @@ int tq1_linear_swiglu_f16(const uint8_t *blocks, const void *x, void *y, int y_i
 #define TQ1_KERNEL_TENSOR_CORE 2
 int tq1_linear_plan(int M, int N, int K, int aligned, int *kernel, int *token_tile, int *ctas, int *parts);
 
-/* For recording sweeps only: force the tensor-core kernel's token tile (16..256) for every
- * later call of this process; 0 restores the rule. Not thread-safe. No reference counterpart. */
-int tq1_debug_force_token_tile(int token_tile);
-
 /* ---- row-sharded linear over several GPUs -------------------------------- */
 
 /* One rank's view of an output-row shard. Output rows are independent, so rank r owns rows
@@ -201,6 +197,24 @@ int tq1_gemv_f16_noalloc(const uint8_t *blocks, const void *x, void *y, int y_is
                          int N, int K, void *stream);
 int tq1_gemv_noalloc_status(uint32_t *status_host, void *stream);
 
+/* ---- streaming layout for batch-1 decoding ---------------------------------- */
+
+/* Chunk-major panels: the same 28-byte blocks, permuted once at load so that the 16 rows x 4 groups a
+ * warp consumes at a time are 1792 CONTIGUOUS bytes:
+ *     panels[c][r][112]   c = K/512 column chunks, r = rows padded with zero blocks to a multiple of 16,
+ *                         112 bytes = the four blocks of row r in columns [512c, 512c + 512)
+ * On B200 a fetch of sixteen 112-byte row pieces 1120+ bytes apart (canonical layout) sustains 3.7 TB/s,
+ * a contiguous 1792-byte copy 6.8 TB/s. The reference likewise permutes the canonical blocks into a
+ * kernel-friendly device form at load (reorder_tensor_arrays, src/bonsai_tq1/lut23_reorder.py:126-165;
+ * pack_blocks, src/ternel_mlx/packing.py:51-82); the permutation is lossless and
+ * tq1_panels_to_blocks_device restores the canonical bytes exactly. Needs K % 512 == 0 and 16-byte
+ * aligned pointers. Chain links accept either form (tq1_chain_link.layout). */
+#define TQ1_LAYOUT_BLOCKS 0
+#define TQ1_LAYOUT_PANELS 1
+size_t tq1_panel_bytes(int N, int K);
+int tq1_blocks_to_panels_device(const uint8_t *blocks, uint8_t *panels, int N, int K, void *stream);
+int tq1_panels_to_blocks_device(const uint8_t *panels, uint8_t *blocks, int N, int K, void *stream);
+
 /* ---- a chain of batch-1 products in one launch ----------------------------- */
 
 /* A decoded token runs one matrix-vector product per packed linear, back to back: the
@@ -216,7 +230,7 @@ int tq1_gemv_noalloc_status(uint32_t *status_host, void *stream);
  * elements, is rounded to FP16 for any later link that reads it, and is stored to y (FP16 or
  * FP32) when y is not NULL. */
 typedef struct tq1_chain_link {
-    const uint8_t *blocks; /* device, canonical [N][K/128][28], 16-byte aligned; this rank's rows */
+    const uint8_t *blocks; /* device, canonical [N][K/128][28] (or panels, see layout), 16-byte aligned; this rank's rows */
     int N, K;              /* K % 512 == 0, K <= 65536 */
     const void *x;         /* device FP16 [K], complete before the launch; NULL: read link `source` */
     int source;            /* with x == NULL: index of an EARLIER link whose output is this link's input */
@@ -225,6 +239,7 @@ typedef struct tq1_chain_link {
     int y_is_f32;
     int swiglu;            /* rows are (gate, up) pairs: N/2 outputs */
     float out_scale;       /* multiplies every output; 0 is taken as 1 */
+    int layout;            /* TQ1_LAYOUT_BLOCKS: `blocks` is canonical; TQ1_LAYOUT_PANELS: it is the panel form below */
 } tq1_chain_link;
 
 /* Row-sharded chains: every rank runs the same list over its own rows of every matrix (rank r owns

@@ -36,13 +36,15 @@ SIGNATURES = {
                                       c_void_p, c_size_t, c_void_p]),
     "tq1_linear_plan": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int),
                                 POINTER(c_int)]),
-    "tq1_debug_force_token_tile": (c_int, [c_int]),
     "tq1_linear_sharded_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tq1_shard_advance_epoch": (c_int, [c_void_p, ctypes.c_uint32, c_void_p]),
     "tq1_linear_f16_sharded": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t,
                                        c_void_p]),
     "tq1_gemv_f16_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tq1_gemv_noalloc_status": (c_int, [c_void_p, c_void_p]),
+    "tq1_panel_bytes": (c_size_t, [c_int, c_int]),
+    "tq1_blocks_to_panels_device": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "tq1_panels_to_blocks_device": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "tq1_chain_workspace_bytes": (c_size_t, [c_void_p, c_int, c_int]),
     "tq1_chain_handoff_bytes": (c_size_t, [c_void_p, c_int, c_int]),
     "tq1_chain_table_bytes": (c_size_t, [c_void_p, c_int]),
@@ -70,7 +72,7 @@ class ChainLink(ctypes.Structure):
     _fields_ = [
         ("blocks", c_void_p), ("N", c_int), ("K", c_int), ("x", c_void_p), ("source", c_int),
         ("source_offset", c_int), ("y", c_void_p), ("y_is_f32", c_int), ("swiglu", c_int),
-        ("out_scale", ctypes.c_float),
+        ("out_scale", ctypes.c_float), ("layout", c_int),
     ]
 
 

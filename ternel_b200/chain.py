@@ -29,7 +29,8 @@ class Link:
 
     ``x``: FP16 ``[K]`` tensor complete before the launch, or ``None`` to read the output of link
     ``source`` (an earlier link) starting at element ``source_offset``. ``y``: optional output tensor
-    (FP16 or FP32, ``N`` elements, ``N/2`` with ``swiglu``).
+    (FP16 or FP32, ``N`` elements, ``N/2`` with ``swiglu``). With ``panel_rows > 0`` ``blocks`` holds the
+    chunk-major panel form of ``blocks_to_panels`` for a weight of that many rows.
     """
 
     blocks: torch.Tensor
@@ -39,14 +40,15 @@ class Link:
     y: torch.Tensor | None = None
     swiglu: bool = False
     out_scale: float = 1.0
+    panel_rows: int = 0
 
     @property
     def rows(self) -> int:
-        return self.blocks.shape[0]
+        return self.panel_rows if self.panel_rows else self.blocks.shape[0]
 
     @property
     def columns(self) -> int:
-        return self.blocks.shape[1] * BLOCK_SIZE
+        return self.blocks.shape[0] * 512 if self.panel_rows else self.blocks.shape[1] * BLOCK_SIZE
 
     @property
     def outputs(self) -> int:
@@ -57,7 +59,12 @@ def _pack_links(links: list[Link]):
     array = (_native.ChainLink * len(links))()
     for i, link in enumerate(links):
         b = link.blocks
-        if b.dtype != torch.uint8 or b.dim() != 3 or b.shape[2] != BLOCK_BYTES or not b.is_contiguous():
+        if link.panel_rows:
+            pad = (link.panel_rows + 15) // 16 * 16
+            if b.dtype != torch.uint8 or b.dim() != 3 or b.shape[1] != pad or b.shape[2] != 112 or not b.is_contiguous():
+                raise FormatError(f"link {i}: panels of {link.panel_rows} rows must be contiguous uint8 "
+                                  f"(chunks, {pad}, 112), got {tuple(b.shape)}")
+        elif b.dtype != torch.uint8 or b.dim() != 3 or b.shape[2] != BLOCK_BYTES or not b.is_contiguous():
             raise FormatError(f"link {i}: blocks must be contiguous uint8 (rows, groups, 28), got {tuple(b.shape)}")
         if not b.is_cuda:
             raise RuntimeError(f"link {i}: blocks are on {b.device}; the packed ternary kernels run on CUDA only")
@@ -80,7 +87,40 @@ def _pack_links(links: list[Link]):
         else:
             c.y, c.y_is_f32 = None, 0
         c.swiglu, c.out_scale = int(link.swiglu), float(link.out_scale)
+        c.layout = 1 if link.panel_rows else 0
     return array
+
+
+def blocks_to_panels(blocks: torch.Tensor) -> torch.Tensor:
+    """Canonical ``uint8[N, K/128, 28]`` on the GPU -> chunk-major panels ``uint8[K/512, pad16(N), 112]`` (a
+    lossless permutation, rows padded with zero blocks): the layout the chain streams fastest."""
+    if blocks.dtype != torch.uint8 or blocks.dim() != 3 or blocks.shape[2] != BLOCK_BYTES or not blocks.is_contiguous():
+        raise FormatError(f"blocks must be contiguous uint8 (rows, groups, 28), got {tuple(blocks.shape)}")
+    if not blocks.is_cuda:
+        raise RuntimeError(f"blocks are on {blocks.device}; the packed ternary kernels run on CUDA only")
+    rows, columns = blocks.shape[0], blocks.shape[1] * BLOCK_SIZE
+    if columns % 512:
+        raise FormatError(f"{columns} columns is not a multiple of 512")
+    out = torch.empty((columns // 512, (rows + 15) // 16 * 16, 112), dtype=torch.uint8, device=blocks.device)
+    with torch.cuda.device(blocks.device):
+        check(_native.lib().tq1_blocks_to_panels_device(
+            blocks.data_ptr(), out.data_ptr(), rows, columns,
+            ctypes.c_void_p(torch.cuda.current_stream(blocks.device).cuda_stream)))
+    return out
+
+
+def panels_to_blocks(panels: torch.Tensor, rows: int) -> torch.Tensor:
+    """The inverse of ``blocks_to_panels``: the canonical blocks, byte for byte."""
+    if panels.dtype != torch.uint8 or panels.dim() != 3 or panels.shape[2] != 112 or not panels.is_contiguous() \
+            or panels.shape[1] != (rows + 15) // 16 * 16:
+        raise FormatError(f"panels of {rows} rows must be contiguous uint8 (chunks, pad16(rows), 112), got {tuple(panels.shape)}")
+    columns = panels.shape[0] * 512
+    out = torch.empty((rows, columns // BLOCK_SIZE, BLOCK_BYTES), dtype=torch.uint8, device=panels.device)
+    with torch.cuda.device(panels.device):
+        check(_native.lib().tq1_panels_to_blocks_device(
+            panels.data_ptr(), out.data_ptr(), rows, columns,
+            ctypes.c_void_p(torch.cuda.current_stream(panels.device).cuda_stream)))
+    return out
 
 
 def linear_chain(links: list[Link], workspace: torch.Tensor) -> None:

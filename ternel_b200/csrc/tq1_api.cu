@@ -76,6 +76,9 @@ int tq1_linear_plan(int M, int N, int K, int aligned, int *kernel, int *token_ti
     return TQ1_OK;
 }
 
+// Sweep recording only (ternel_b200/dispatch.py binds it by name): forces the tensor-core kernel's token tile
+// for every later call of this process; 0 restores the rule. Process-global and not thread-safe, which is why
+// it is not part of the public header.
 int tq1_debug_force_token_tile(int token_tile) {
     if (gemm_tc_force_tile(token_tile) != TQ1_OK)
         return fail(TQ1_ERR_INVALID, "tq1_debug_force_token_tile: %d is not 0, 16, 32, 64, 128 or 256", token_tile);

@@ -87,7 +87,7 @@ using namespace tq1;
 
 extern "C" {
 
-int tq1_abi_version(void) { return 1; }
+int tq1_abi_version(void) { return 2; }
 
 const char *tq1_last_error(void) { return g_error; }
 

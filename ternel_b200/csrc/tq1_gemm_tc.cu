@@ -59,7 +59,9 @@ __host__ __device__ constexpr int gemm_stages(int nt) { return nt > 128 ? 3 : nt
 // The decode table is replicated per lane (8-byte entries x 32 lanes, conflict-free) except for the
 // 256-token tile: there the tensor cores set the pace, the lookups' bank conflicts are hidden, and
 // the 60 KB saved by a single copy of the table pay for a third 64 KB activation stage.
-__host__ __device__ constexpr int gemm_lut_bytes(int nt) { return nt > 128 ? 2048 : 243 * 256; }
+// 256 entries (the 13 past 242 decode to zero weights): the table is indexed by the raw code byte, so a byte
+// that escaped the load-time scan still reads inside the table instead of past the CTA's shared memory.
+__host__ __device__ constexpr int gemm_lut_bytes(int nt) { return nt > 128 ? 2048 : 256 * 256; }
 __host__ __device__ constexpr int gemm_tmem_cols(int nt) { return nt <= 16 ? 256 : 512; }
 // packed-byte buffers (4 K blocks each): small activation tiles leave room for a deep prefetch queue,
 // which is what hides HBM latency when the tensor work per K block is tiny
@@ -76,7 +78,7 @@ __host__ __device__ constexpr int perm_column(int p) {
 // An 8-bit selector picks the two bytes of one FP16 value out of the pool
 // [0x00, s_lo, s_hi, s_hi ^ 0x80]: code 0 -> -s = (1,3), code 1 -> 0 = (0,0), code 2 -> +s = (1,2).
 struct GemmLutImage {
-    uint32_t w[243 * 64];
+    uint32_t w[256 * 64];
 };
 constexpr uint32_t sel8(uint32_t c) { return c == 0 ? 0x31u : c == 1 ? 0x00u : 0x21u; }
 constexpr GemmLutImage make_gemm_lut() {
@@ -686,15 +688,22 @@ EncodeTiledFn gemm_encode_fn() {
     return fn;
 }
 
+// Launch state is per DEVICE: the SM count differs between devices and the shared-memory opt-in is an
+// attribute of a function on one device, so a process that drives several GPUs needs one record each.
+constexpr int kMaxDevices = 64;
+int current_device_slot() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    return dev;
+}
 int sm_count_cached() {
-    static int sm_count = 0;
-    if (!sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
-            sm_count = 148;
+    static int sm_count[kMaxDevices] = {};
+    const int dev = current_device_slot();
+    if (!sm_count[dev]) {
+        if (cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count[dev] <= 0)
+            sm_count[dev] = 148;
     }
-    return sm_count;
+    return sm_count[dev];
 }
 
 // How the (tile, K block) iterations of a shape are dealt out for a given token tile.
@@ -778,12 +787,13 @@ size_t gemm_smem_bytes() {
 template <int NT, bool PERSIST>
 int launch_nt(const CUtensorMap &wmap, const CUtensorMap &xmap, const GemmParams &prm, dim3 grid, cudaStream_t stream) {
     auto kern = tq1_gemm_tc_kernel<NT, PERSIST>;
-    static bool attr_set = false;
+    static bool attr_set[kMaxDevices] = {};
     const size_t smem = gemm_smem_bytes<NT>();
-    if (!attr_set) {
+    const int dev = current_device_slot();
+    if (!attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return cuda_fail(e, "tq1_linear_f16: shared memory opt-in (GEMM)");
-        attr_set = true;
+        attr_set[dev] = true;
     }
     kern<<<grid, gemm_threads(NT, PERSIST), smem, stream>>>(wmap, xmap, prm);
     cudaError_t err = cudaGetLastError();

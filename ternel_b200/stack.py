@@ -110,7 +110,7 @@ class LayerStack:
     def __init__(self, *, layers: int, batch: int = 1, shape: LayerShape = LayerShape(),
                  vocab: int = 0, rank: int = 0, world: int = 1, device=None, seed: int = 0,
                  group=None, fused: bool = False, exchange: str = "chain", dependent: bool = True,
-                 weights_from: "LayerStack | None" = None) -> None:
+                 panels: bool = True, weights_from: "LayerStack | None" = None) -> None:
         self.layers, self.batch, self.shape = layers, batch, shape
         self.rank, self.world, self.group = rank, world, group
         self.device = torch.device(device if device is not None else "cuda")
@@ -128,6 +128,7 @@ class LayerStack:
             raise ValueError("the chain runs batch 1; use exchange='launches' for larger batches")
         self.exchange = exchange
         self.dependent = dependent and exchange == "chain"
+        self.use_panels = panels and exchange == "chain"
         # weights[l][j]: this rank's rows [rank*N/P, (rank+1)*N/P) of projection j in layer l
         if weights_from is not None:       # a second stack (another batch size) over the same resident weights
             if (weights_from.projections, weights_from.world, weights_from.layers) != (self.projections, world, layers):
@@ -163,9 +164,14 @@ class LayerStack:
             self.workspace_bytes = ws_bytes
 
     # ------------------------------------------------------------------
-    def chain_links(self, layers: "int | None" = None):
-        """The step as chain links over this rank's weight shards (see the module docstring)."""
-        from .chain import Link
+    def chain_links(self, layers: "int | None" = None, panels: "bool | None" = None):
+        """The step as chain links over this rank's weight shards (see the module docstring). With ``panels`` the
+        links stream the chunk-major panel copies of the weights instead of the canonical blocks."""
+        from .chain import Link, blocks_to_panels
+        panels = self.use_panels if panels is None else panels
+        if panels and not hasattr(self, "panels"):
+            # a second, permuted copy of every weight (the canonical one stays for the batched kernels and the oracle)
+            self.panels = [[blocks_to_panels(w) for w in layer] for layer in self.weights]
         shape, world = self.shape, self.world
         hidden = shape.hidden
         links, outs = [], []
@@ -180,7 +186,10 @@ class LayerStack:
                 swiglu = self.dependent and name == "gate_up"
                 n_out = (n // 2 if swiglu else n) // world
                 y = torch.zeros(n_out, dtype=torch.float16, device=self.device)
-                link = Link(blocks=blocks[j], y=y, swiglu=swiglu)
+                if panels:
+                    link = Link(blocks=self.panels[layer][j], panel_rows=n // world, y=y, swiglu=swiglu)
+                else:
+                    link = Link(blocks=blocks[j], y=y, swiglu=swiglu)
                 if not self.dependent:
                     link.x = self.inputs[k][0]
                     link.out_scale = unit_gain(k)
@@ -206,6 +215,10 @@ class LayerStack:
                     link.out_scale = unit_gain(k)
                 links.append(link)
                 outs.append(y)
+        scales = getattr(self, "link_scales", None)          # measured at set-up (see _calibrate)
+        if scales is not None and self.dependent:
+            for link, scale in zip(links, scales):
+                link.out_scale = scale
         return links, outs
 
     def _calibrate(self, links) -> None:
@@ -225,7 +238,8 @@ class LayerStack:
                 x = link.x
             else:
                 x = gathered[link.source][link.source_offset: link.source_offset + link.columns]
-            y = tq1_matmul(link.blocks, x.reshape(1, -1).contiguous(), out_dtype=torch.float32)[0]
+            canonical = self.weights[i // len(self.projections)][i % len(self.projections)]   # the link may stream a permuted copy
+            y = tq1_matmul(canonical, x.reshape(1, -1).contiguous(), out_dtype=torch.float32)[0]
             if link.swiglu:
                 gate, up = y[0::2], y[1::2]
                 y = gate / (1.0 + torch.exp(-gate)) * up
@@ -250,6 +264,7 @@ class LayerStack:
         links, self.link_outputs = self.chain_links()
         if self.dependent:
             self._calibrate(links)
+            self.link_scales = [link.out_scale for link in links]
         peers = None
         if self.world > 1:
             import torch.distributed as dist

@@ -218,3 +218,90 @@ def test_bad_links_are_refused_before_any_launch():
         ChainPlan([Link(blocks=b, x=x), Link(blocks=b, source=0)])         # 256 outputs cannot feed K = 1024
     with pytest.raises((FormatError, ValueError)):
         ChainPlan([Link(blocks=to_dev(random_blocks(256, 640, seed=1)[0]), x=x[:640].contiguous())])   # K % 512
+
+
+@pytest.mark.parametrize(("rows", "columns"), ((16, 512), (300, 1536), (1024, 5120), (5000, 2048)))
+def test_panel_layout_is_a_lossless_permutation(rows, columns):
+    """blocks -> panels -> blocks restores every byte; a panel is the chunk's [rows][112] slice, zero padded."""
+    from ternel_b200.chain import blocks_to_panels, panels_to_blocks
+    blocks, _ = random_blocks(rows, columns, seed=rows + columns, dist="tests")
+    dev = to_dev(blocks)
+    panels = blocks_to_panels(dev)
+    torch.cuda.synchronize()
+    host = panels.cpu().numpy()
+    pad = (rows + 15) // 16 * 16
+    assert host.shape == (columns // 512, pad, 112)
+    want = blocks.reshape(rows, columns // 512, 112).transpose(1, 0, 2)
+    assert np.array_equal(host[:, :rows], want)
+    assert not host[:, rows:].any()
+    back = panels_to_blocks(panels, rows)
+    torch.cuda.synchronize()
+    assert np.array_equal(back.cpu().numpy(), blocks)
+
+
+def test_chain_over_panels_equals_chain_over_canonical_blocks():
+    """The same dependent chain streamed from either layout gives bit-identical outputs."""
+    from ternel_b200.chain import ChainPlan, Link, blocks_to_panels
+    rng = np.random.default_rng(77)
+    shapes = ((1536, 1024), (1000, 1536), (2048, 512), (48, 2048))        # ragged row counts, several chunks
+    x = to_dev(rng.standard_normal(1024).astype(np.float16))
+    weights = [to_dev(random_blocks(n, k, seed=900 + i)[0]) for i, (n, k) in enumerate(shapes)]
+    results = []
+    for use_panels in (False, True):
+        links, outs = [], []
+        for i, ((n, k), w) in enumerate(zip(shapes, weights)):
+            y = torch.zeros(n, dtype=torch.float32, device="cuda")
+            outs.append(y)
+            kwargs = dict(x=x) if i == 0 else dict(source=i - 1)
+            if use_panels:
+                links.append(Link(blocks=blocks_to_panels(w), panel_rows=n, y=y, out_scale=2.0, **kwargs))
+            else:
+                links.append(Link(blocks=w, y=y, out_scale=2.0, **kwargs))
+        plan = ChainPlan(links)
+        for _ in range(2):
+            plan.run()
+        torch.cuda.synchronize()
+        assert plan.status() == 0
+        results.append([y.cpu().numpy() for y in outs])
+    for a, b in zip(*results):
+        assert np.isfinite(a).all() and np.abs(a).max() > 0
+        assert np.array_equal(a, b)
+
+
+def test_row_shards_are_pushed_into_every_ranks_hand_off_area():
+    """Two ranks emulated one after the other on one GPU (a kernel here never waits for the other rank): each runs
+    a one-link chain over its half of the rows with both hand-off areas as peers. Afterwards BOTH areas hold the
+    whole output as {FP16 bits, tag} words and each rank's y holds its own rows."""
+    import ctypes
+    from ternel_b200 import _native
+    from ternel_b200.chain import ChainPlan, Link
+    lib = _native.lib()
+    rows, columns = 1024, 1536
+    blocks, rng = random_blocks(rows, columns, seed=314)
+    x = rng.standard_normal(columns).astype(np.float16)
+    want = o.float64_matmul(blocks, x[None, :], rows=rows, columns=columns)[0]
+    xd = to_dev(x)
+    half = rows // 2
+    shards = [to_dev(blocks[:half]), to_dev(blocks[half:])]
+    ys = [torch.zeros(half, dtype=torch.float16, device="cuda") for _ in range(2)]
+    probe = [Link(blocks=shards[0], x=xd, y=ys[0])]
+    from ternel_b200.chain import _pack_links
+    nbytes = lib.tq1_chain_handoff_bytes(_pack_links(probe), 1, 2)
+    areas = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    plans = [ChainPlan([Link(blocks=shards[r], x=xd, y=ys[r])], peers=(r, 2, [a.data_ptr() for a in areas]))
+             for r in range(2)]
+    for step in range(2):
+        for r in range(2):
+            plans[r].run()
+        torch.cuda.synchronize()
+        for r in range(2):
+            assert plans[r].status() == 0
+            got = ys[r].float().cpu().numpy()
+            assert o.normalised_error(got[None, :], want[None, r * half:(r + 1) * half]) < 2e-3
+        full = np.concatenate([ys[0].cpu().numpy(), ys[1].cpu().numpy()])
+        for area in areas:
+            words = area[: rows * 8].view(torch.int64).cpu().numpy()
+            values = (words & 0xffff).astype(np.uint16).view(np.float16)
+            tags = (words >> 32).astype(np.uint32)
+            assert np.array_equal(values, full)                  # every row, from both ranks, in both areas
+            assert len(set(tags.tolist())) == 1 and tags[0] == step + 1      # one tag per call of the chain
