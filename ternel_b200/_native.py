@@ -8,6 +8,8 @@ PyTorch path.
 from __future__ import annotations
 
 import ctypes
+import os
+from pathlib import Path
 from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p, POINTER
 
 from .build import LIB_PATH
@@ -83,6 +85,10 @@ class ChainPeers(ctypes.Structure):
 
 _lib: ctypes.CDLL | None = None
 
+# TERNEL_B200_LIBRARY names another build of the same C ABI to load instead (the bounds-checking build,
+# _lib/libternel_b200_checked.so, is the intended use). It is read once, at the first call.
+LIBRARY_ENV = "TERNEL_B200_LIBRARY"
+
 
 class NativeLibraryMissing(RuntimeError):
     pass
@@ -92,18 +98,34 @@ def lib() -> ctypes.CDLL:
     """The loaded library; raises loudly if it has not been built."""
     global _lib
     if _lib is None:
-        if not LIB_PATH.exists():
+        path = Path(os.environ.get(LIBRARY_ENV) or LIB_PATH)
+        if not path.exists():
             raise NativeLibraryMissing(
-                f"{LIB_PATH} is missing: build it with `python -m ternel_b200.build` "
+                f"{path} is missing: build it with `python -m ternel_b200.build` "
                 "(there is no CPU or PyTorch fallback for the packed ternary kernels)"
             )
-        handle = ctypes.CDLL(str(LIB_PATH))
+        handle = ctypes.CDLL(str(path))
         for name, (restype, argtypes) in SIGNATURES.items():
             fn = getattr(handle, name)
             fn.restype = restype
             fn.argtypes = argtypes
+        if hasattr(handle, "tq1_debug_bounds"):         # exported by the bounds-checking build only
+            handle.tq1_debug_bounds.restype = c_int
+            handle.tq1_debug_bounds.argtypes = [POINTER(ctypes.c_uint64)]
         _lib = handle
     return _lib
+
+
+def bounds_record() -> "tuple[int, int, int, int] | None":
+    """(violations, code of the first, its index, its limit) since the last call, or None when the loaded
+    library is not the bounds-checking build. Reading clears the record."""
+    handle = lib()
+    if not hasattr(handle, "tq1_debug_bounds"):
+        return None
+    record = (ctypes.c_uint64 * 4)()
+    if handle.tq1_debug_bounds(record) != TQ1_OK:
+        raise RuntimeError("tq1_debug_bounds: the record could not be read")
+    return tuple(int(v) for v in record)
 
 
 def last_error() -> str:

@@ -9,6 +9,12 @@
 
 #include "tq1_common.cuh"
 
+#ifdef TQ1_BOUNDS_CHECK
+namespace tq1 {
+__device__ unsigned long long g_tq1_bounds[4] = {0, 0, 0, 0};
+}
+#endif
+
 namespace tq1 {
 
 static thread_local char g_error[512] = "";
@@ -88,6 +94,16 @@ using namespace tq1;
 extern "C" {
 
 int tq1_abi_version(void) { return 2; }
+
+#ifdef TQ1_BOUNDS_CHECK
+// {violations, code of the first, its index, its limit}; copies the record to host memory and clears it.
+int tq1_debug_bounds(unsigned long long *out_host) {
+    if (cudaMemcpyFromSymbol(out_host, tq1::g_tq1_bounds, sizeof(unsigned long long) * 4) != cudaSuccess) return TQ1_ERR_CUDA;
+    const unsigned long long zero[4] = {0, 0, 0, 0};
+    if (cudaMemcpyToSymbol(tq1::g_tq1_bounds, zero, sizeof(zero)) != cudaSuccess) return TQ1_ERR_CUDA;
+    return TQ1_OK;
+}
+#endif
 
 const char *tq1_last_error(void) { return g_error; }
 

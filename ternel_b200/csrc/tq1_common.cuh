@@ -25,6 +25,29 @@ constexpr size_t kWsStatusBytes = 256;
 constexpr size_t kWsSlotRegionBytes = (size_t)16 << 20;
 constexpr size_t kWsScratchOffset = kWsStatusBytes + kWsSlotRegionBytes;
 
+// Checked build (-DTQ1_BOUNDS_CHECK -rdc=true): every global store of a kernel (and the reads of scratch that
+// other CTAs write) first tests its index against the extent the launcher knows. A violation is counted in
+// g_tq1_bounds {count, code of the first, its index, its limit} and the access is SKIPPED: the kernel neither
+// traps nor touches memory it does not own. The reference's analogue is the SAFE build of its Metal kernels,
+// which clamps row indices (src/ternel_mlx/kernels.py:23-27). tq1_debug_bounds() reads the record.
+// Codes: 1x chain kernel (10 slot store, 11 slot read, 12 y, 13 hand-off store, 14 hand-off read),
+// 2x row kernel, 3x gather, 4x batched kernel (40 result, 41 partial tile), 5x panels, 6x shard push.
+#ifdef TQ1_BOUNDS_CHECK
+extern __device__ unsigned long long g_tq1_bounds[4];
+__device__ __forceinline__ bool tq1_in_bounds(long long index, long long limit, unsigned code) {
+    if (index >= 0 && index < limit) return true;
+    if (atomicAdd(&g_tq1_bounds[0], 1ull) == 0ull) {
+        g_tq1_bounds[1] = code;
+        g_tq1_bounds[2] = (unsigned long long)index;
+        g_tq1_bounds[3] = (unsigned long long)limit;
+    }
+    return false;
+}
+#define TQ1_IN_BOUNDS(index, limit, code) tq1_in_bounds((long long)(index), (long long)(limit), (code))
+#else
+#define TQ1_IN_BOUNDS(index, limit, code) true
+#endif
+
 // Records a message for tq1_last_error() and returns `code`.
 int fail(int code, const char *fmt, ...);
 int cuda_fail(cudaError_t err, const char *what);

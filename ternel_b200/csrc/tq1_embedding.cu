@@ -83,6 +83,7 @@ embedding_kernel(const uint8_t *__restrict__ blocks, const int64_t *__restrict__
         const float c0 = live[q] ? -1.0f * scale : 0.0f, c1 = live[q] ? 0.0f * scale : 0.0f,
                     c2 = live[q] ? 1.0f * scale : 0.0f;
         const size_t base = ((size_t)(t0 + q) * gpr + g) * kGroup + 8 * j;
+        if (!TQ1_IN_BOUNDS(base + 7, (size_t)T * gpr * kGroup, 30u)) continue;
         if (OUT_F32) {
             float v[8];
 #pragma unroll

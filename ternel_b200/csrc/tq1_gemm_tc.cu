@@ -370,6 +370,7 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     if (c0 + c < NT && m < prm.M && n + 1 < prm.N && (r & 1) == 0) {
                         const float out = swiglu_f32(gate, up);
                         const size_t o = (size_t)m * (prm.N >> 1) + (n >> 1);
+                        if (!TQ1_IN_BOUNDS(o, (size_t)prm.M * (prm.N >> 1), 40u)) continue;
                         if (prm.y_f32) static_cast<float *>(prm.y)[o] = out;
                         else static_cast<__half *>(prm.y)[o] = __float2half_rn(out);
                     }
@@ -389,6 +390,9 @@ tq1_gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 const int m = m0 + c0 + c;
                 if (c0 + c < NT && m < prm.M && n < prm.N) {
                     const float f = __uint_as_float(v[c]);
+                    if (!TQ1_IN_BOUNDS(whole ? (size_t)m * prm.N + n : (size_t)(c0 + c) * kTileW + r,
+                                       whole ? (size_t)prm.M * prm.N : (size_t)NT * kTileW, whole ? 40u : 41u))
+                        continue;
                     if (!whole)
                         slot[(c0 + c) * kTileW + r] = f;
                     else if (prm.y_f32)

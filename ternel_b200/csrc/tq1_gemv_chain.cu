@@ -505,7 +505,8 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
                 const bool live = prep && chunk_lo + cl <= chunk_hi;
                 const unsigned long long *xc = xin + (size_t)(chunk_lo + cl) * kChunkCols;
-                wv[cl] = live ? word_read(xc + tid) : ((unsigned long long)want << 32);
+                wv[cl] = live && TQ1_IN_BOUNDS((chunk_lo + cl) * kChunkCols + tid, chunks * kChunkCols, 14u)
+                             ? word_read(xc + tid) : ((unsigned long long)want << 32);
             }
 #pragma unroll
             for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
@@ -700,7 +701,8 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             // quad: lanes q=0 (groups 0,1) and q=2 (groups 2,3) -> chunk partial in lane q=0
             acc1 += __shfl_down_sync(0xffffffffu, acc1, 2);
             acc2 += __shfl_down_sync(0xffffffffu, acc2, 2);
-            if (q == 0) {       // value and tag travel in one 64-bit store, so whoever sees the tag has the value
+            if (q == 0 && TQ1_IN_BOUNDS((mine - slots) + 8, P.region_slots, 10u)) {
+                // value and tag travel in one 64-bit store, so whoever sees the tag has the value
                 slot_publish(mine, acc1, tag);
                 slot_publish(mine + 8, acc2, tag);
             }
@@ -726,7 +728,8 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             int cc = R.c_first, tt = R.t_first;
             int tm = R.t_first % chunks;                 // tt % chunks, kept up to date without dividing again
             for (int i = 0; i < n_units; ++i) {
-                if (tm == cc) {                          // warp-uniform: this warp owns row tile tt
+                if (tm == cc && TQ1_IN_BOUNDS((size_t)tt * kTileRows + r + (size_t)(chunks - 1) * stride, P.region_slots, 11u)) {
+                    // warp-uniform: this warp owns row tile tt
                     const unsigned long long *ps = slots + (size_t)tt * kTileRows + r;
                     float total = 0.0f;
                     for (int c0 = hf; c0 < chunks; c0 += 16) {
@@ -758,7 +761,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                         row >>= 1;
                     }
                     total *= out_scale;
-                    if (writer) {
+                    if (writer && TQ1_IN_BOUNDS(row, swiglu ? N >> 1 : N, 12u)) {
                         const __half hv = __float2half_rn(total);
                         if (y) {
                             if (out_f32) static_cast<float *>(y)[row] = total;

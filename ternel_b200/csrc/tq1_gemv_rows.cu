@@ -95,6 +95,7 @@ __global__ void __launch_bounds__(kRowsThreads) gemv_rows_kernel(const uint8_t *
             a += __shfl_xor_sync(0xffffffffu, a, 8);
             a += __shfl_xor_sync(0xffffffffu, a, 16);
             if (lane == 0) {
+                if (!TQ1_IN_BOUNDS(row, N, 20u)) continue;
                 if (OUT_F32) static_cast<float *>(y)[(int64_t)m * ldy + row] = a;
                 else static_cast<__half *>(y)[(int64_t)m * ldy + row] = __float2half_rn(a);
             }

@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(256) panels_kernel(const uint4 *__restrict__ s
         const int j = (int)(rem - r * kPanelRowVecs);
         const long long canon = r * row_vecs + c * kPanelRowVecs + j;
         if (TO_PANELS) dst[i] = r < rows ? src[canon] : make_uint4(0u, 0u, 0u, 0u);
-        else if (r < rows) dst[canon] = src[i];
+        else if (r < rows && TQ1_IN_BOUNDS(canon, rows * row_vecs, 50u)) dst[canon] = src[i];
     }
 }
 

@@ -37,6 +37,7 @@ __global__ void __launch_bounds__(256) tq1_shard_push_kernel(const __half *__res
         for (int i = lane; i < M * kFlagRows; i += 32) {
             const int m = i / kFlagRows, n = tile * kFlagRows + (i - m * kFlagRows);
             const __half v = local[(size_t)m * n_local + n];
+            if (!TQ1_IN_BOUNDS(n, n_local, 60u)) continue;
             for (int p = 0; p < shard.world; ++p) shard.peer_y[p][(size_t)m * shard.ld_total + n] = v;
         }
         __threadfence_system();          // every lane's stores are performed before any flag below
