@@ -107,7 +107,9 @@ size_t tq1_linear_workspace_bytes(int M, int N, int K);
  *             and 512-wide K chunk: the value and a sequence tag in one 64-bit
  *             word, so nothing is ever cleared), then the scratch of the
  *             M >= 2 kernels. After a non-zero status, zero-fill the workspace
- *             again.
+ *             again. Status 7 is not a failure: the results are good, but the
+ *             32-bit sequence tags have passed 0xF0000000 executed projections
+ *             and the workspace must be zero-filled before they wrap.
  * The kernel is chosen from M: 1 => streaming GEMV, 2..16 => small-batch
  * split-K GEMV, larger => tiled GEMM. Illegal code bytes must have been
  * rejected at load (tq1_validate_blocks*): the kernels carry no clamp. */

@@ -93,7 +93,9 @@ static_assert(kWindowEnd + kHighBytes <= 227 * 1024, "shared memory budget");
 constexpr uint32_t kMaxWaitSpins = 1u << 21;
 
 // Control words at the start of the workspace.
-constexpr int kCtlStatus = 0;      // non-zero: a bounded wait ran out (1 tile, 4 hand-off word, 5 slot, 6 region)
+constexpr int kCtlStatus = 0;      // non-zero: a bounded wait ran out (1 tile, 4 hand-off word, 5 slot, 6 region);
+                                   // 7: results are good, but the tag base has passed kTagRefresh
+constexpr unsigned kTagRefresh = 0xF0000000u;
 constexpr int kCtlExit = 1;        // CTAs that have left the current launch
 constexpr int kCtlEpoch = 2;       // links executed by all earlier launches on this workspace (tag base)
 constexpr int kCtlArrive = 3;      // [2] CTAs that are done with the slots of the links of each region
@@ -790,6 +792,9 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             ctl[kCtlArrive] = 0u;
             ctl[kCtlArrive + 1] = 0u;
             ctl[kCtlEpoch] = tag_base + P.tag_advance;
+            // Tags are 32-bit: long before they could wrap onto values that old slots still carry, ask the
+            // caller (through the status word) to zero the workspace between two launches.
+            if (tag_base + P.tag_advance >= kTagRefresh) atomicCAS(ctl + kCtlStatus, 0u, 7u);
         }
     }
 }
