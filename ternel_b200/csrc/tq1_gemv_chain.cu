@@ -66,12 +66,21 @@ constexpr int kUnitBytes = kTileRows * kChunkBytes;           // 1792
 #define TQ1_GEMV_STAGES 4
 #endif
 constexpr int kStages = TQ1_GEMV_STAGES;
-constexpr int kWarps = TQ1_GEMV_WARPS;           // the first 16 also prepare the activations (one thread each)
-constexpr int kPrepThreads = 512;
+constexpr int kWarps = TQ1_GEMV_WARPS;           // warp w < 4 * (chunks of the CTA) also prepares activation group w
 constexpr int kThreads = kWarps * 32;
 constexpr int kMaxChunksPerCta = 3;
+constexpr int kPrepWarps = 4 * kMaxChunksPerCta;               // one warp per 128-activation group
 constexpr int kRegsPerSub = 18;                                // A/B registers per lane per sub-unit
-static_assert(kWarps >= 16, "sixteen warps prepare the activations");
+static_assert(kWarps >= kPrepWarps, "one warp per activation group of the CTA's chunks");
+
+// Per activation group, written by the warp that prepared it: 121 * (sum of the fifth-trit activations),
+// 2^(E-21) for the group's exponent E, and whether the group holds NaN/Inf.
+struct alignas(16) GroupConst {
+    int sum;
+    float pow;
+    int bad;
+    int pad;
+};
 
 // Shared-memory window layout (addresses relative to the CTA's shared window). The table sits
 // at a 64 KiB multiple so that PRMT can build a complete lookup address
@@ -81,13 +90,16 @@ constexpr uint32_t kLutWindowAddr = 131072;
 constexpr uint32_t kLutBytes = 256 * 256;                     // 256 entries x (2 x 32 lanes x 4 B)
 constexpr uint32_t kWindowEnd = kLutWindowAddr + kLutBytes;   // 196608
 constexpr uint32_t kRingBytes = kWarps * kStages * kUnitBytes;                     // 114688
-constexpr uint32_t kBtabOne = kMaxChunksPerCta * 2 * kRegsPerSub * 32 * 4;         // 13824 per buffer
+constexpr uint32_t kBtabChunk = 2 * kRegsPerSub * 32 * 4;                          // 4608: digit planes of one chunk
+constexpr uint32_t kBtabOne = kMaxChunksPerCta * kBtabChunk;                       // 13824 per buffer
 constexpr uint32_t kBtabBytes = 2 * kBtabOne;                                      // two links in flight
 constexpr uint32_t kMbarBytes = 8 * (kWarps * kStages + 2);
-constexpr uint32_t kRedOne = 3 * 4 * 16 * kMaxChunksPerCta;                        // group max / sum / non-finite
-constexpr uint32_t kRedBytes = 2 * kRedOne;
-constexpr uint32_t kXsBytes = kMaxChunksPerCta * kChunkCols * 4;                    // the CTA's activations as FP32
-constexpr uint32_t kHighBytes = kBtabBytes + kMbarBytes + kRedBytes + kXsBytes;
+constexpr uint32_t kGconstOne = kPrepWarps * sizeof(GroupConst);
+constexpr uint32_t kGconstBytes = 2 * kGconstOne;
+constexpr uint32_t kXchgBytes = kPrepWarps * kGroup * 4;                           // a warp's fixed-point activations
+constexpr uint32_t kPrepTabBytes = kGroup * 4;                                     // where activation e of a group goes
+constexpr uint32_t kMiscBytes = 16;
+constexpr uint32_t kHighBytes = kBtabBytes + kMbarBytes + kGconstBytes + kXchgBytes + kPrepTabBytes + kMiscBytes;
 static_assert(kRingBytes + 1024 + 128 <= kLutWindowAddr, "the ring must end below the table's fixed address");
 static_assert(kWindowEnd + kHighBytes <= 227 * 1024, "shared memory budget");
 constexpr uint32_t kMaxWaitSpins = 1u << 21;
@@ -335,15 +347,22 @@ __device__ __forceinline__ WarpRange warp_range(int tiles, int units_q, int unit
     const int b = (int)blockIdx.x;
     const int cta_begin = b * units_q + min(b, units_r);
     const int cta_units = units_q + (b < units_r ? 1 : 0);
-    const int cta_end = cta_begin + cta_units;
-    const float inv = __frcp_rn((float)tiles);
     r.u_begin = cta_begin + (cta_units * warp) / kWarps;
     const int u_end = cta_begin + (cta_units * (warp + 1)) / kWarps;
     r.n_units = u_end - r.u_begin;
-    r.chunk_lo = cta_units > 0 ? div_tiles(cta_begin, tiles, inv) : 0;
-    r.chunk_hi = cta_units > 0 ? div_tiles(cta_end - 1, tiles, inv) : -1;
-    r.c_first = div_tiles(r.u_begin, tiles, inv);
-    r.t_first = r.u_begin - r.c_first * tiles;
+    // one division for the CTA; a CTA spans at most kMaxChunksPerCta chunks, so the rest is comparisons
+    r.chunk_lo = div_tiles(cta_begin, tiles, __frcp_rn((float)tiles));
+    const int base = r.chunk_lo * tiles;
+    int last = cta_begin + cta_units - 1 - base, hi = r.chunk_lo;
+    int first = r.u_begin - base, cf = r.chunk_lo;
+#pragma unroll
+    for (int k = 1; k < kMaxChunksPerCta; ++k) {
+        if (last >= tiles) { last -= tiles; ++hi; }
+        if (first >= tiles) { first -= tiles; ++cf; }
+    }
+    r.chunk_hi = cta_units > 0 ? hi : r.chunk_lo - 1;
+    r.c_first = cf;
+    r.t_first = first;
     return r;
 }
 
@@ -354,8 +373,11 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
     unsigned char *high = smem + (kWindowEnd - window);
     uint32_t *btab_all = reinterpret_cast<uint32_t *>(high);
     uint64_t *mbars = reinterpret_cast<uint64_t *>(high + kBtabBytes);
-    unsigned char *red_all = high + kBtabBytes + kMbarBytes;
-    float *xs = reinterpret_cast<float *>(high + kBtabBytes + kMbarBytes + kRedBytes);   // [chunk][activation]
+    GroupConst *gconst_all = reinterpret_cast<GroupConst *>(high + kBtabBytes + kMbarBytes);      // [buffer][group]
+    int *xchg = reinterpret_cast<int *>(high + kBtabBytes + kMbarBytes + kGconstBytes) + (threadIdx.x >> 5) * kGroup;
+    uint32_t *preptab = reinterpret_cast<uint32_t *>(high + kBtabBytes + kMbarBytes + kGconstBytes + kXchgBytes);
+    volatile int *region_ok = reinterpret_cast<volatile int *>(high + kBtabBytes + kMbarBytes + kGconstBytes +
+                                                               kXchgBytes + kPrepTabBytes);
     unsigned *ctl = P.ctl;
     if (window + kRingBytes > kLutWindowAddr) {      // the fixed-address table would overlap the ring
         if (threadIdx.x == 0) atomicExch(ctl + kCtlStatus, 2u);
@@ -438,28 +460,30 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
     // byte offset of this lane's first half-block inside a tile (sub-unit 0, row g)
     const uint32_t lane_tile_off = (uint32_t)(((g * kChunkGroups + 2 * cls) * kBlockWords + 3 * h) * 4);
 
-    // activation roles of the prologue: one thread per activation of a chunk
-    const int gi = tid >> 7;                           // group within the chunk
-    const int el = tid & 127;
-    const int bj = el < 125 ? el / 5 : 25;             // code byte
-    const int bi = el < 125 ? el - 5 * bj : el - 125;  // trit within the byte
-    const bool is_fifth = el < 125 && bi == 4;         // pairs with the raw code byte
-    const int fifth = el < 125 ? gi * kGroup + 5 * bj + 4 : tid;
-    uint32_t plane_off;                                // byte offset of this activation's digit 0 inside a chunk's planes
-    {
-        const int hh = bj < 14 ? 0 : 1;                    // which half-block lane decodes it
+    // Where activation e of a group goes. Trits 0..3 of code byte j sit in the table-entry register of the
+    // byte's slot; a fifth trit pairs with the raw word. Entry: byte offset of digit 0 inside a group's planes
+    // (bits 0..15), index of the byte's fifth-trit activation (16..23, 255: the tail byte has none) and 3^i
+    // (24..31, 0 for a fifth trit).
+    if (tid < kGroup) {
+        const int el = tid;
+        const int bj = el < 125 ? el / 5 : 25;             // code byte
+        const int bi = el < 125 ? el - 5 * bj : el - 125;  // trit within the byte
+        const bool is_fifth = el < 125 && bi == 4;
+        const int hh = bj < 14 ? 0 : 1;                    // which half-block lane decodes the byte
         const int slot = hh ? bj - 12 : bj;
-        // trits 0..3 sit in the table-entry register of their slot; a fifth trit pairs with the raw word
         const int reg = !is_fifth ? slot : slot < 2 ? 14 : 15 + ((slot - 2) >> 2);
         const int pos = !is_fifth ? bi : slot < 2 ? slot + 2 : ((slot - 2) & 3);
-        const int sub = gi & 1, cg = gi >> 1;
-        const int owner = 4 * (4 * cg) + 2 * cg + hh;      // B lane of digit plane 0; plane p is 4p lanes on
-        plane_off = (uint32_t)((((sub * kRegsPerSub + reg) * 32 + owner) * 4) + pos);
+        const uint32_t off = (uint32_t)((reg * 32 + hh) * 4 + pos);
+        const uint32_t fifth = el < 125 ? (uint32_t)(5 * bj + 4) : 255u;
+        const uint32_t pow3 = is_fifth ? 0u : bi == 0 ? 1u : bi == 1 ? 3u : bi == 2 ? 9u : 27u;
+        preptab[el] = off | (fifth << 16) | (pow3 << 24);
     }
-    const int pow3 = bi == 0 ? 1 : bi == 1 ? 3 : bi == 2 ? 9 : 27;
+    if (tid == 0) *region_ok = 0;
+    // planes of group gi of a chunk: sub-unit gi & 1, B lanes 18 * (gi >> 1) + {0, 1} (+ 4 per digit plane)
+    const uint32_t warp_plane_off = (uint32_t)(((warp & 1) * kRegsPerSub * 32 + 18 * ((warp >> 1) & 1)) * 4);
 
     bool dead = false;                                 // a bounded wait ran out: stop waiting, finish quickly
-    __syncthreads();                                   // barriers initialised, planes zeroed
+    __syncthreads();                                   // barriers initialised, planes zeroed, table written
     PHASE_DECL
 
     for (int p = 0; p < n_links; ++p) {
@@ -472,75 +496,106 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         const int n_units = R.n_units, chunk_lo = R.chunk_lo, chunk_hi = R.chunk_hi;
         const int buf = p & 1;
         uint32_t *btab = btab_all + buf * (kBtabOne / 4);
-        float *red_max = reinterpret_cast<float *>(red_all + buf * kRedOne);       // [chunk][warp]
-        int *red_sum = reinterpret_cast<int *>(red_max + kMaxChunksPerCta * 16);
-        int *red_bad = red_sum + kMaxChunksPerCta * 16;
+        GroupConst *gconst = gconst_all + buf * kPrepWarps;
         const unsigned tag = tag_base + (unsigned)L.tag + 1u;
-        // Read the region's arrival counter now (checked after the first barrier below): its round trip then
-        // overlaps the wait for the activations instead of sitting between the two barriers.
+        // Read the region's arrival counter now (checked after the barrier below): its round trip then
+        // overlaps the wait for the activations.
         unsigned arrived_early = 0u;
         if (tid == 0 && p >= 2 && P.n_regions > 1) arrived_early = ctl_read(ctl + kCtlArrive + (p & 1));
 
-        // ---- this CTA's activations: one thread per activation, which also fetches the activation
-        // of the fifth trit of its code byte (needed for 81 x_i - 3^i x_4) -----------------------------
-        const bool prep = tid < kPrepThreads;
-        float xv[kMaxChunksPerCta];
-        if (xin == nullptr) {
+        // ---- activation digits: warp w prepares group w & 3 of the CTA's chunk w >> 2, four activations per
+        // lane: group maximum, fixed point, four signed byte planes. All reductions stay inside the warp. ------
+        if (warp < 4 * (chunk_hi - chunk_lo + 1)) {
+            const int cl = warp >> 2;
+            const size_t x0 = (size_t)(chunk_lo + cl) * kChunkCols + (size_t)(warp & 3) * kGroup + lane;
+            float xv[4];
+            if (xin == nullptr) {
 #pragma unroll
-            for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
-                const bool live = prep && chunk_lo + cl <= chunk_hi;
-                const __half *xc = xh + (size_t)(chunk_lo + cl) * kChunkCols;
-                xv[cl] = live ? __half2float(xc[tid]) : 0.0f;
+                for (int k = 0; k < 4; ++k) xv[k] = __half2float(xh[x0 + 32 * k]);
+                // The activation loads are in flight: now top up this warp's weight tiles (issued the other
+                // way round the few activation bytes queue behind megabytes of weight traffic).
+                if (lane == 0)
+                    while (issued - consumed < kStages - 1 && issue_one()) {}
+            } else {
+                // Output of an earlier link: keep the weight pipeline full, then wait (bounded) for exactly the
+                // words this lane needs.
+                if (lane == 0)
+                    while (issued - consumed < kStages - 1 && issue_one()) {}
+                const unsigned want = tag_base + (unsigned)L.src_tag + 1u;
+                unsigned long long wv[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    wv[k] = TQ1_IN_BOUNDS(x0 + 32 * k, (size_t)chunks * kChunkCols, 14u)
+                                ? word_read(xin + x0 + 32 * k) : ((unsigned long long)want << 32);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    uint32_t spins = 0;
+                    while ((unsigned)(wv[k] >> 32) != want && !dead) {
+                        if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 4u); dead = true; break; }
+                        wv[k] = word_read(xin + x0 + 32 * k);
+                    }
+                    xv[k] = __half2float(__ushort_as_half((unsigned short)(wv[k] & 0xffffu)));
+                }
             }
-            // The activation loads are in flight: now start this warp's weight tiles (issued the other
-            // way round the few activation bytes queue behind megabytes of weight traffic). One tile
-            // per warp for now, so that every warp's first tile is near the head of the queue.
-            if (lane == 0 && issued == consumed) issue_one();
+            PHASE(0)
+            // non-negative floats order like their bit patterns: one redux instruction for the group maximum
+            unsigned mbits = 0u;
+            bool bad[4], anybad = false;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float a = fabsf(xv[k]);
+                bad[k] = !(a <= 65504.0f);                         // NaN or Inf
+                anybad = anybad || bad[k];
+                mbits = max(mbits, bad[k] ? 0u : __float_as_uint(a));
+            }
+            mbits = __reduce_max_sync(0xffffffffu, mbits);
+            const int group_bad = __any_sync(0xffffffffu, anybad);
+            // 2^E <= m < 2^(E+1); fixed point xi = round(v * 2^(21-E)), |xi| <= 2^22
+            const int e_biased = mbits != 0u ? (int)(mbits >> 23) : 127;
+            const float up = __uint_as_float((uint32_t)(275 - e_biased) << 23);                // 2^(21-E)
+            int xi[4], s5 = 0;
+            uint32_t ent[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                xi[k] = bad[k] ? 0 : __float2int_rn(xv[k] * up);
+                xchg[lane + 32 * k] = xi[k];                       // a code byte's first four trits need its fifth
+                ent[k] = preptab[lane + 32 * k];
+                s5 += (ent[k] >> 24) == 0u ? 121 * xi[k] : 0;      // 121 * sum of the fifth-trit activations
+            }
+            s5 = __reduce_add_sync(0xffffffffu, s5);
+            if (lane == 0) {
+                GroupConst gc;
+                gc.sum = s5;
+                gc.pow = __uint_as_float((uint32_t)(e_biased - 21) << 23);                     // 2^(E-21)
+                gc.bad = group_bad;
+                gc.pad = 0;
+                gconst[warp] = gc;
+            }
+            __syncwarp();
+            unsigned char *planes = reinterpret_cast<unsigned char *>(btab) + cl * kBtabChunk + warp_plane_off;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                // value paired with this k-slot: x_4 for the raw byte, 81 x_i - 3^i x_4 for trit i < 4
+                const uint32_t fifth = (ent[k] >> 16) & 0xffu;
+                const int x4 = fifth != 255u ? xchg[fifth] : 0;
+                const int pw = (int)(ent[k] >> 24);
+                const int v = pw ? 81 * xi[k] - pw * x4 : xi[k];
+                // four signed byte digits: the bytes of v + 0x80808080 are the digits plus 128
+                const uint32_t d = ((uint32_t)v + 0x80808080u) ^ 0x80808080u;
+                unsigned char *base = planes + (ent[k] & 0xffffu);
+                base[0] = (unsigned char)d;
+                base[16] = (unsigned char)(d >> 8);
+                base[32] = (unsigned char)(d >> 16);
+                base[48] = (unsigned char)(d >> 24);
+            }
         } else {
-            // Output of an earlier link: keep the weight pipeline full, then wait (bounded) for exactly the
-            // words this thread needs.
             if (lane == 0)
                 while (issued - consumed < kStages - 1 && issue_one()) {}
-            const unsigned want = tag_base + (unsigned)L.src_tag + 1u;
-            unsigned long long wv[kMaxChunksPerCta];
-#pragma unroll
-            for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
-                const bool live = prep && chunk_lo + cl <= chunk_hi;
-                const unsigned long long *xc = xin + (size_t)(chunk_lo + cl) * kChunkCols;
-                wv[cl] = live && TQ1_IN_BOUNDS((chunk_lo + cl) * kChunkCols + tid, chunks * kChunkCols, 14u)
-                             ? word_read(xc + tid) : ((unsigned long long)want << 32);
-            }
-#pragma unroll
-            for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
-                const unsigned long long *xc = xin + (size_t)(chunk_lo + cl) * kChunkCols;
-                uint32_t spins = 0;
-                while ((unsigned)(wv[cl] >> 32) != want && !dead) {
-                    if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 4u); dead = true; break; }
-                    wv[cl] = word_read(xc + tid);
-                }
-                xv[cl] = __half2float(__ushort_as_half((unsigned short)(wv[cl] & 0xffffu)));
-            }
+            PHASE(0)
         }
-
-        PHASE(0)
-        // ---- activation digits: group maximum, fixed point, four signed byte planes --------------------
-        bool bad[kMaxChunksPerCta];
-        const int n_chunks_cta = chunk_hi - chunk_lo + 1;
-        if (prep) {
-#pragma unroll
-            for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
-                if (cl >= n_chunks_cta) break;
-                const float a = fabsf(xv[cl]);
-                bad[cl] = !(a <= 65504.0f);                        // NaN or Inf
-                // non-negative floats order like their bit patterns: one redux instruction per warp
-                const unsigned m = __reduce_max_sync(0xffffffffu, bad[cl] ? 0u : __float_as_uint(a));
-                const int anybad = __any_sync(0xffffffffu, bad[cl]);
-                xs[cl * kChunkCols + tid] = xv[cl];                // the threads of a code byte's first four trits need its fifth
-                if (lane == 0) { red_max[cl * 16 + warp] = __uint_as_float(m); red_bad[cl * 16 + warp] = anybad; }
-            }
-        }
-        __syncthreads();
         PHASE(4)
+        __syncthreads();
+        PHASE(5)
         // Every warp of this CTA has left link p-1, so the CTA is done with that link's slots; and
         // before anybody publishes into the region link p shares with link p-2, every CTA must be
         // done with link p-2's slots.
@@ -553,43 +608,9 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                     if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 6u); break; }
                 }
             }
-        }
-        // every warp's first tile is on its way: now queue the rest of the ring behind them
-        if (lane == 0)
-            while (issued - consumed < kStages - 1 && issue_one()) {}
-        PHASE(5)
-        if (prep) {
-            const int gw = warp & ~3;                          // the four warps of this thread's group
-#pragma unroll
-            for (int cl = 0; cl < kMaxChunksPerCta; ++cl) {
-                if (cl >= n_chunks_cta) break;
-                const float4 rm = *reinterpret_cast<const float4 *>(red_max + cl * 16 + gw);
-                const float m = fmaxf(fmaxf(rm.x, rm.y), fmaxf(rm.z, rm.w));
-                // 2^E <= m < 2^(E+1); fixed point xi = round(v * 2^(21-E)), |xi| <= 2^22
-                const int e_biased = m > 0.0f ? (int)(__float_as_uint(m) >> 23) : 127;
-                const float up = __uint_as_float((uint32_t)(275 - e_biased) << 23);            // 2^(21-E)
-                const int xi = bad[cl] ? 0 : __float2int_rn(xv[cl] * up);
-                // 121 * sum of the fifth-trit activations of this warp's 32 activations
-                const int s = __reduce_add_sync(0xffffffffu, is_fifth ? 121 * xi : 0);
-                if (lane == 0) red_sum[cl * 16 + warp] = s;
-                // value paired with this k-slot: x_4 for the raw byte, 81 x_i - 3^i x_4 for trit i < 4
-                int v = xi;
-                if (!is_fifth) {
-                    const float x4f = xs[cl * kChunkCols + fifth];
-                    const int x4 = (el < 125 && fabsf(x4f) <= 65504.0f) ? __float2int_rn(x4f * up) : 0;
-                    v = 81 * xi - pow3 * x4;
-                }
-                // four signed byte digits: the bytes of v + 0x80808080 are the digits plus 128
-                const uint32_t d = ((uint32_t)v + 0x80808080u) ^ 0x80808080u;
-                unsigned char *base = reinterpret_cast<unsigned char *>(btab) + cl * (2 * kRegsPerSub * 32 * 4) + plane_off;
-                base[0] = (unsigned char)d;
-                base[16] = (unsigned char)(d >> 8);
-                base[32] = (unsigned char)(d >> 16);
-                base[48] = (unsigned char)(d >> 24);
-            }
+            *region_ok = p + 1;
         }
         PHASE(6)
-        __syncthreads();
 
         PHASE(1)
         if (p == 0) {                                   // the decode table must have landed
@@ -609,6 +630,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         int c = R.c_first, t = R.t_first;
         // slot of row g of the current unit: units are numbered chunk-major, so it advances by 16 per unit
         unsigned long long *mine = slots + (size_t)R.u_begin * kTileRows + g;
+        bool region_checked = !(p >= 2 && P.n_regions > 1);
 
         for (int i = 0; i < n_units; ++i) {
             if (c != cur_chunk) {       // (re)load the B fragments and the group constants of this K chunk
@@ -619,12 +641,17 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
 #pragma unroll
                     for (int r = 0; r < kRegsPerSub; ++r)
                         breg[sub][r] = btab[((cl * 2 + sub) * kRegsPerSub + r) * 32 + lane];
-                    const int w4 = cl * 16 + 4 * (sub + 2 * cls);              // the group's four warps
-                    gsum[sub] = red_sum[w4] + red_sum[w4 + 1] + red_sum[w4 + 2] + red_sum[w4 + 3];
-                    const float gm = fmaxf(fmaxf(red_max[w4], red_max[w4 + 1]), fmaxf(red_max[w4 + 2], red_max[w4 + 3]));
-                    const int eb = gm > 0.0f ? (int)(__float_as_uint(gm) >> 23) : 127;
-                    gpow[sub] = __uint_as_float((uint32_t)(eb - 21) << 23);                    // 2^(E-21)
-                    gbad[sub] = red_bad[w4] | red_bad[w4 + 1] | red_bad[w4 + 2] | red_bad[w4 + 3];
+                    const GroupConst gc = gconst[cl * 4 + sub + 2 * cls];
+                    gsum[sub] = gc.sum;
+                    gpow[sub] = gc.pow;
+                    gbad[sub] = gc.bad;
+                }
+                if (!region_checked) {  // thread 0 has seen every CTA leave the link that used these slots last
+                    region_checked = true;
+                    uint32_t spins = 0;
+                    while (*region_ok < p + 1 && !dead) {
+                        if (++spins > kMaxWaitSpins) { if (lane == 0) atomicExch(ctl + kCtlStatus, 6u); dead = true; }
+                    }
                 }
             }
             const uint32_t s = (uint32_t)consumed % kStages;
