@@ -411,20 +411,23 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
 
     // ---- producer cursor: the next unit this warp requests, possibly of a later link ------------------
     int issued = 0, consumed = 0;               // units requested / finished by this warp since the launch began
-    int iss_link = 0, iss_left, iss_c, iss_t, iss_tiles;
+    int iss_link = 0, iss_left, iss_t, iss_tiles;
+    int iss_x, iss_y;                           // canonical layout: TMA coordinates of the next unit
     const CUtensorMap *iss_map;
-    const unsigned char *iss_panel;             // non-null: the link's weights are panels
-    size_t iss_panel_stride;                    // bytes from one chunk's panel to the next
+    const unsigned char *iss_src;               // panels: the next unit's 1792 bytes (null: canonical layout)
+    size_t iss_wrap;                            // panels: extra bytes from a chunk's last tile to the next chunk's first
     auto cursor_load = [&]() {
         const ChainLinkDev &L = links[iss_link];
         const WarpRange r = warp_range(L.tiles, L.units_q, L.units_r, warp);
-        iss_left = r.n_units; iss_c = r.c_first; iss_t = r.t_first; iss_tiles = L.tiles;
+        iss_left = r.n_units; iss_t = r.t_first; iss_tiles = L.tiles;
+        iss_x = r.c_first * kChunkBytes; iss_y = r.t_first * kTileRows;
         iss_map = &L.wmap;
-        iss_panel = nullptr;
+        iss_src = nullptr;
         if (L.flags & kFlagPanels) {
             const PanelRef *ref = reinterpret_cast<const PanelRef *>(&L.wmap);
-            iss_panel = ref->base;
-            iss_panel_stride = (size_t)ref->pad_rows * kChunkBytes;
+            const size_t stride = (size_t)ref->pad_rows * kChunkBytes;
+            iss_src = ref->base + (size_t)r.c_first * stride + (size_t)r.t_first * kUnitBytes;
+            iss_wrap = stride - (size_t)L.tiles * kUnitBytes;
         }
     };
     cursor_load();
@@ -436,17 +439,22 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         }
         const uint32_t s = (uint32_t)issued % kStages;
         mbar_expect_tx(bar0 + 8u * s, kUnitBytes);
-        if (iss_panel)      // one contiguous bulk copy: measured 6.8 TB/s against 3.7 TB/s for the strided 112-byte rows
-            bulk_load(ring_warp + s * kUnitBytes, iss_panel + (size_t)iss_c * iss_panel_stride + (size_t)iss_t * kUnitBytes,
-                      kUnitBytes, bar0 + 8u * s);
-        else
-            tma_load_2d(ring_warp + s * kUnitBytes, iss_map, iss_c * kChunkBytes, iss_t * kTileRows, bar0 + 8u * s);
+        if (iss_src) {      // one contiguous bulk copy: measured 6.8 TB/s against 3.7 TB/s for the strided 112-byte rows
+            bulk_load(ring_warp + s * kUnitBytes, iss_src, kUnitBytes, bar0 + 8u * s);
+            iss_src += kUnitBytes;
+        } else {
+            tma_load_2d(ring_warp + s * kUnitBytes, iss_map, iss_x, iss_y, bar0 + 8u * s);
+            iss_y += kTileRows;
+        }
         ++issued;
         --iss_left;
-        if (++iss_t == iss_tiles) { iss_t = 0; ++iss_c; }
+        if (++iss_t == iss_tiles) {
+            iss_t = 0; iss_y = 0; iss_x += kChunkBytes;
+            if (iss_src) iss_src += iss_wrap;
+        }
         return true;
     };
-    if (tid == 0 && !iss_panel) asm volatile("prefetch.tensormap [%0];" ::"l"(iss_map) : "memory");
+    if (tid == 0 && !iss_src) asm volatile("prefetch.tensormap [%0];" ::"l"(iss_map) : "memory");
 
     // Let the next kernel in the stream start its own prologue as SMs free up, then wait until
     // everything before this kernel has finished before touching activations or the workspace.
@@ -626,117 +634,123 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         int gsum[2];
         float gpow[2];
         int gbad[2];
-        int cur_chunk = -1;
         int c = R.c_first, t = R.t_first;
         // slot of row g of the current unit: units are numbered chunk-major, so it advances by 16 per unit
         unsigned long long *mine = slots + (size_t)R.u_begin * kTileRows + g;
         bool region_checked = !(p >= 2 && P.n_regions > 1);
+        auto slow_wait = [&](uint32_t bar, uint32_t parity) -> uint32_t {     // the tile was not there at the first look
+            uint32_t arrived = 0, spins = 0;
+            while (!dead && !(arrived = mbar_try_wait(bar, parity))) {
+                if (++spins > kMaxWaitSpins) {          // never hang: flag the failure and stop waiting
+                    if (lane == 0) atomicExch(ctl + kCtlStatus, 1u);
+                    dead = true;
+                }
+            }
+            return arrived;
+        };
 
-        for (int i = 0; i < n_units; ++i) {
-            if (c != cur_chunk) {       // (re)load the B fragments and the group constants of this K chunk
-                cur_chunk = c;
-                const int cl = c - chunk_lo;
-#pragma unroll
-                for (int sub = 0; sub < 2; ++sub) {
-#pragma unroll
-                    for (int r = 0; r < kRegsPerSub; ++r)
-                        breg[sub][r] = btab[((cl * 2 + sub) * kRegsPerSub + r) * 32 + lane];
-                    const GroupConst gc = gconst[cl * 4 + sub + 2 * cls];
-                    gsum[sub] = gc.sum;
-                    gpow[sub] = gc.pow;
-                    gbad[sub] = gc.bad;
-                }
-                if (!region_checked) {  // thread 0 has seen every CTA leave the link that used these slots last
-                    region_checked = true;
-                    uint32_t spins = 0;
-                    while (*region_ok < p + 1 && !dead) {
-                        if (++spins > kMaxWaitSpins) { if (lane == 0) atomicExch(ctl + kCtlStatus, 6u); dead = true; }
-                    }
-                }
-            }
-            const uint32_t s = (uint32_t)consumed % kStages;
-            const uint32_t parity = ((uint32_t)consumed / kStages) & 1u;
-            uint32_t arrived = 0;
-            if (!dead) {
-                uint32_t spins = 0;
-                while (!(arrived = mbar_try_wait(bar0 + 8u * s, parity))) {
-                    if (++spins > kMaxWaitSpins) {          // never hang: flag the failure and stop waiting
-                        if (lane == 0) atomicExch(ctl + kCtlStatus, 1u);
-                        dead = true;
-                        break;
-                    }
-                }
-            }
-            // (arrived >> 8) is zero, but only the hardware knows: the tile loads depend on the wait
-            const uint32_t tile_addr = ring_warp + s * kUnitBytes + (arrived >> 8);
-            const uint32_t a1 = tile_addr + lane_tile_off;
-            float acc1 = 0.0f, acc2 = 0.0f;             // rows g and g+8, this lane's two groups
+        for (int left = n_units; left > 0;) {
+            // ---- (re)load the B fragments and the group constants of this K chunk ----------------------
+            const int cl = c - chunk_lo;
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
-                constexpr int kRow8 = 8 * kChunkBytes;
-                const uint32_t w1a = sub ? lds_off<28>(a1) : lds_off<0>(a1);
-                const uint32_t w1b = sub ? lds_off<32>(a1) : lds_off<4>(a1);
-                const uint32_t w1c = sub ? lds_off<36>(a1) : lds_off<8>(a1);
-                const uint32_t w1d = sub ? lds_off<40>(a1) : lds_off<12>(a1);
-                const uint32_t w2a = sub ? lds_off<kRow8 + 28>(a1) : lds_off<kRow8 + 0>(a1);
-                const uint32_t w2b = sub ? lds_off<kRow8 + 32>(a1) : lds_off<kRow8 + 4>(a1);
-                const uint32_t w2c = sub ? lds_off<kRow8 + 36>(a1) : lds_off<kRow8 + 8>(a1);
-                const uint32_t w2d = sub ? lds_off<kRow8 + 40>(a1) : lds_off<kRow8 + 12>(a1);
-                uint32_t r1[kRegsPerSub], r2[kRegsPerSub];
-                decode_stream(w1a, w1b, w1c, w1d, lane_base, r1);
-                decode_stream(w2a, w2b, w2c, w2d, lane_base, r2);
-                // two independent accumulator chains; register pairs 0..6 hold signed weights,
-                // pairs 7,8 the raw (unsigned) code bytes
-                int accA[4], accB[4];
-                mma_bytes<true, true>(accA, r1[0], r2[0], r1[1], r2[1], breg[sub][0], breg[sub][1]);
-                mma_bytes<true, true>(accB, r1[2], r2[2], r1[3], r2[3], breg[sub][2], breg[sub][3]);
-                mma_bytes<true, false>(accA, r1[4], r2[4], r1[5], r2[5], breg[sub][4], breg[sub][5]);
-                mma_bytes<true, false>(accB, r1[6], r2[6], r1[7], r2[7], breg[sub][6], breg[sub][7]);
-                mma_bytes<true, false>(accA, r1[8], r2[8], r1[9], r2[9], breg[sub][8], breg[sub][9]);
-                mma_bytes<true, false>(accB, r1[10], r2[10], r1[11], r2[11], breg[sub][10], breg[sub][11]);
-                mma_bytes<true, false>(accA, r1[12], r2[12], r1[13], r2[13], breg[sub][12], breg[sub][13]);
-                mma_bytes<false, false>(accB, r1[14], r2[14], r1[15], r2[15], breg[sub][14], breg[sub][15]);
-                mma_bytes<false, false>(accA, r1[16], r2[16], r1[17], r2[17], breg[sub][16], breg[sub][17]);
-                // columns: lane q=0 holds planes 0,1 of the first group, q=1 planes 2,3; q=2/3 the second group.
-                // Combine each lane's plane pair first, then one shuffle per row brings the upper pair over.
-                const uint32_t pair1 = (uint32_t)(accA[0] + accB[0]) + ((uint32_t)(accA[1] + accB[1]) << 8);
-                const uint32_t pair2 = (uint32_t)(accA[2] + accB[2]) + ((uint32_t)(accA[3] + accB[3]) << 8);
-                const uint32_t hi1 = __shfl_down_sync(0xffffffffu, pair1, 1);
-                const uint32_t hi2 = __shfl_down_sync(0xffffffffu, pair2, 1);
-                if (h == 0) {
+#pragma unroll
+                for (int r = 0; r < kRegsPerSub; ++r)
+                    breg[sub][r] = btab[((cl * 2 + sub) * kRegsPerSub + r) * 32 + lane];
+                const GroupConst gc = gconst[cl * 4 + sub + 2 * cls];
+                gsum[sub] = gc.sum;
+                gpow[sub] = gc.pow;
+                gbad[sub] = gc.bad;
+            }
+            const bool chunk_bad = __any_sync(0xffffffffu, (gbad[0] | gbad[1]) != 0);
+            if (!region_checked) {      // thread 0 has seen every CTA leave the link that used these slots last
+                region_checked = true;
+                uint32_t spins = 0;
+                while (*region_ok < p + 1 && !dead) {
+                    if (++spins > kMaxWaitSpins) { if (lane == 0) atomicExch(ctl + kCtlStatus, 6u); dead = true; }
+                }
+            }
+            const int seg = min(left, tiles - t);       // units of this chunk
+            left -= seg;
+            for (int i = 0; i < seg; ++i) {
+                const uint32_t s = (uint32_t)consumed % kStages;
+                const uint32_t parity = ((uint32_t)consumed / kStages) & 1u;
+                uint32_t arrived = mbar_try_wait(bar0 + 8u * s, parity);
+                if (!arrived) arrived = slow_wait(bar0 + 8u * s, parity);
+                // (arrived >> 8) is zero, but only the hardware knows: the tile loads depend on the wait
+                const uint32_t tile_addr = ring_warp + s * kUnitBytes + (arrived >> 8);
+                const uint32_t a1 = tile_addr + lane_tile_off;
+                float acc1 = 0.0f, acc2 = 0.0f;             // rows g and g+8, this lane's two groups
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub) {
+                    constexpr int kRow8 = 8 * kChunkBytes;
+                    const uint32_t w1a = sub ? lds_off<28>(a1) : lds_off<0>(a1);
+                    const uint32_t w1b = sub ? lds_off<32>(a1) : lds_off<4>(a1);
+                    const uint32_t w1c = sub ? lds_off<36>(a1) : lds_off<8>(a1);
+                    const uint32_t w1d = sub ? lds_off<40>(a1) : lds_off<12>(a1);
+                    const uint32_t w2a = sub ? lds_off<kRow8 + 28>(a1) : lds_off<kRow8 + 0>(a1);
+                    const uint32_t w2b = sub ? lds_off<kRow8 + 32>(a1) : lds_off<kRow8 + 4>(a1);
+                    const uint32_t w2c = sub ? lds_off<kRow8 + 36>(a1) : lds_off<kRow8 + 8>(a1);
+                    const uint32_t w2d = sub ? lds_off<kRow8 + 40>(a1) : lds_off<kRow8 + 12>(a1);
+                    uint32_t r1[kRegsPerSub], r2[kRegsPerSub];
+                    decode_stream(w1a, w1b, w1c, w1d, lane_base, r1);
+                    decode_stream(w2a, w2b, w2c, w2d, lane_base, r2);
+                    // two independent accumulator chains; register pairs 0..6 hold signed weights,
+                    // pairs 7,8 the raw (unsigned) code bytes
+                    int accA[4], accB[4];
+                    mma_bytes<true, true>(accA, r1[0], r2[0], r1[1], r2[1], breg[sub][0], breg[sub][1]);
+                    mma_bytes<true, true>(accB, r1[2], r2[2], r1[3], r2[3], breg[sub][2], breg[sub][3]);
+                    mma_bytes<true, false>(accA, r1[4], r2[4], r1[5], r2[5], breg[sub][4], breg[sub][5]);
+                    mma_bytes<true, false>(accB, r1[6], r2[6], r1[7], r2[7], breg[sub][6], breg[sub][7]);
+                    mma_bytes<true, false>(accA, r1[8], r2[8], r1[9], r2[9], breg[sub][8], breg[sub][9]);
+                    mma_bytes<true, false>(accB, r1[10], r2[10], r1[11], r2[11], breg[sub][10], breg[sub][11]);
+                    mma_bytes<true, false>(accA, r1[12], r2[12], r1[13], r2[13], breg[sub][12], breg[sub][13]);
+                    mma_bytes<false, false>(accB, r1[14], r2[14], r1[15], r2[15], breg[sub][14], breg[sub][15]);
+                    mma_bytes<false, false>(accA, r1[16], r2[16], r1[17], r2[17], breg[sub][16], breg[sub][17]);
+                    // columns: lane q=0 holds planes 0,1 of the first group, q=1 planes 2,3; q=2/3 the second group.
+                    // Combine each lane's plane pair first, then one shuffle per row brings the upper pair over.
+                    const uint32_t pair1 = (uint32_t)(accA[0] + accB[0]) + ((uint32_t)(accA[1] + accB[1]) << 8);
+                    const uint32_t pair2 = (uint32_t)(accA[2] + accB[2]) + ((uint32_t)(accA[3] + accB[3]) << 8);
+                    const uint32_t hi1 = __shfl_down_sync(0xffffffffu, pair1, 1);
+                    const uint32_t hi2 = __shfl_down_sync(0xffffffffu, pair2, 1);
+                    // Every lane does the arithmetic (no branch); only the even lanes of a quad hold meaningful
+                    // values, and only theirs are used below.
                     // 81 * (group sum) modulo 2^32, then times 81^-1 modulo 2^32: the exact integer group sum
                     const int s1 = (int)((pair1 + (hi1 << 16) - (uint32_t)gsum[sub]) * 0x781948b1u);
                     const int s2 = (int)((pair2 + (hi2 << 16) - (uint32_t)gsum[sub]) * 0x781948b1u);
                     float dot1 = (float)s1 * gpow[sub];
                     float dot2 = (float)s2 * gpow[sub];
-                    if (gbad[sub]) {
-                        const int group = sub + 2 * cls;
-                        const unsigned char *tile = ring + (warp * kStages + s) * kUnitBytes;
-                        const size_t x0 = ((size_t)c * kChunkGroups + group) * kGroup;
-                        dot1 = block_dot_fp32(tile + (g * kChunkGroups + group) * kBlockBytes, xh, xin, x0);
-                        dot2 = block_dot_fp32(tile + ((g + 8) * kChunkGroups + group) * kBlockBytes, xh, xin, x0);
+                    if (chunk_bad) {                        // warp-uniform and rare: NaN/Inf among the activations
+                        if (h == 0 && gbad[sub]) {
+                            const int group = sub + 2 * cls;
+                            const unsigned char *tile = ring + (warp * kStages + s) * kUnitBytes;
+                            const size_t x0 = ((size_t)c * kChunkGroups + group) * kGroup;
+                            dot1 = block_dot_fp32(tile + (g * kChunkGroups + group) * kBlockBytes, xh, xin, x0);
+                            dot2 = block_dot_fp32(tile + ((g + 8) * kChunkGroups + group) * kBlockBytes, xh, xin, x0);
+                        }
                     }
                     const float sc1 = __half2float(__ushort_as_half((unsigned short)(w1a & 0xffffu)));
                     const float sc2 = __half2float(__ushort_as_half((unsigned short)(w2a & 0xffffu)));
                     acc1 = fmaf(sc1, dot1, acc1);
                     acc2 = fmaf(sc2, dot2, acc2);
                 }
-            }
-            // the stage consumed one iteration ago is free: refill it
-            ++consumed;
-            __syncwarp();
-            if (lane == 0 && issued - consumed < kStages - 1) issue_one();
+                // the stage consumed one iteration ago is free: refill it
+                ++consumed;
+                __syncwarp();
+                if (lane == 0 && issued - consumed < kStages - 1) issue_one();
 
-            // quad: lanes q=0 (groups 0,1) and q=2 (groups 2,3) -> chunk partial in lane q=0
-            acc1 += __shfl_down_sync(0xffffffffu, acc1, 2);
-            acc2 += __shfl_down_sync(0xffffffffu, acc2, 2);
-            if (q == 0 && TQ1_IN_BOUNDS((mine - slots) + 8, P.region_slots, 10u)) {
-                // value and tag travel in one 64-bit store, so whoever sees the tag has the value
-                slot_publish(mine, acc1, tag);
-                slot_publish(mine + 8, acc2, tag);
+                // quad: lanes q=0 (groups 0,1) and q=2 (groups 2,3) -> chunk partial in lane q=0
+                acc1 += __shfl_down_sync(0xffffffffu, acc1, 2);
+                acc2 += __shfl_down_sync(0xffffffffu, acc2, 2);
+                if (q == 0 && TQ1_IN_BOUNDS((mine - slots) + 8, P.region_slots, 10u)) {
+                    // value and tag travel in one 64-bit store, so whoever sees the tag has the value
+                    slot_publish(mine, acc1, tag);
+                    slot_publish(mine + 8, acc2, tag);
+                }
+                mine += kTileRows;
             }
-            mine += kTileRows;
-            if (++t == tiles) { t = 0; ++c; }
+            t = 0;
+            ++c;
         }
 
         PHASE(2)
@@ -754,10 +768,15 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             const float out_scale = L.out_scale;
             void *y = L.y;
             const int world = L.world;
-            int cc = R.c_first, tt = R.t_first;
-            int tm = R.t_first % chunks;                 // tt % chunks, kept up to date without dividing again
-            for (int i = 0; i < n_units; ++i) {
-                if (tm == cc && TQ1_IN_BOUNDS((size_t)tt * kTileRows + r + (size_t)(chunks - 1) * stride, P.region_slots, 11u)) {
+            // The tiles of chunk cc that this warp owns are those with t % chunks == cc: walk them directly.
+            int cc = R.c_first, t0 = R.t_first, tm0 = R.t_first % chunks;
+            for (int left = n_units; left > 0;) {
+                const int seg = min(left, tiles - t0);
+                left -= seg;
+                int first = cc - tm0;
+                if (first < 0) first += chunks;
+                for (int tt = t0 + first; tt < t0 + seg; tt += chunks) {
+                    if (!TQ1_IN_BOUNDS((size_t)tt * kTileRows + 15 + (size_t)(chunks - 1) * stride, P.region_slots, 11u)) continue;   // warp-uniform
                     // warp-uniform: this warp owns row tile tt
                     const unsigned long long *ps = slots + (size_t)tt * kTileRows + r;
                     float total = 0.0f;
@@ -801,8 +820,9 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                             word_publish(L.xout[pr] + row, (uint32_t)__half_as_ushort(hv), tag);
                     }
                 }
-                if (++tm == chunks) tm = 0;
-                if (++tt == tiles) { tt = 0; tm = 0; ++cc; }
+                t0 = 0;
+                tm0 = 0;
+                ++cc;
             }
         }
         PHASE(3)
