@@ -211,9 +211,9 @@ __device__ __forceinline__ void mma_bytes(int (&c)[4], uint32_t a0, uint32_t a1,
                                           uint32_t b0, uint32_t b1) {
     if (ZERO_C) {
         if (SIGNED_A)
-            asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
         else
             asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
@@ -244,6 +244,32 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
+}
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {      // one look, no suspension
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// Called by all 32 lanes with warp-uniform arguments: one elected lane arms the barrier and starts the copy.
+__device__ __forceinline__ void elected_bulk_load(uint32_t dst, const void *src, uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%2], %3;\n\t"
+        "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %3, [%2];\n\t}"
+        ::"r"(dst), "l"(src), "r"(bar), "n"(kUnitBytes) : "memory");
+}
+__device__ __forceinline__ void elected_tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%4], %5;\n\t"
+        "@p cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n\t}"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar), "n"(kUnitBytes) : "memory");
 }
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -366,6 +392,8 @@ __device__ __forceinline__ WarpRange warp_range(int tiles, int units_q, int unit
     return r;
 }
 
+// ALL_PANELS: every link's weights are chunk-major panels, so the 2-D TMA path is compiled out.
+template <bool ALL_PANELS>
 __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __grid_constant__ ChainParams P) {
     extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t window = (uint32_t)__cvta_generic_to_shared(smem);
@@ -423,7 +451,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         iss_x = r.c_first * kChunkBytes; iss_y = r.t_first * kTileRows;
         iss_map = &L.wmap;
         iss_src = nullptr;
-        if (L.flags & kFlagPanels) {
+        if (ALL_PANELS || (L.flags & kFlagPanels)) {
             const PanelRef *ref = reinterpret_cast<const PanelRef *>(&L.wmap);
             const size_t stride = (size_t)ref->pad_rows * kChunkBytes;
             iss_src = ref->base + (size_t)r.c_first * stride + (size_t)r.t_first * kUnitBytes;
@@ -431,30 +459,30 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
         }
     };
     cursor_load();
-    auto issue_one = [&]() -> bool {            // lane 0 only; false when the chain has no unit left for this warp
+    // Called by all 32 lanes (the cursor is warp-uniform); false when the chain has no unit left for this warp.
+    auto issue_one = [&]() -> bool {
         while (iss_left == 0) {
             if (iss_link + 1 >= n_links) return false;
             ++iss_link;
             cursor_load();
         }
         const uint32_t s = (uint32_t)issued % kStages;
-        mbar_expect_tx(bar0 + 8u * s, kUnitBytes);
-        if (iss_src) {      // one contiguous bulk copy: measured 6.8 TB/s against 3.7 TB/s for the strided 112-byte rows
-            bulk_load(ring_warp + s * kUnitBytes, iss_src, kUnitBytes, bar0 + 8u * s);
+        if (ALL_PANELS || iss_src) {      // one contiguous bulk copy: measured 6.8 TB/s against 3.7 TB/s for the strided 112-byte rows
+            elected_bulk_load(ring_warp + s * kUnitBytes, iss_src, bar0 + 8u * s);
             iss_src += kUnitBytes;
         } else {
-            tma_load_2d(ring_warp + s * kUnitBytes, iss_map, iss_x, iss_y, bar0 + 8u * s);
+            elected_tma_load_2d(ring_warp + s * kUnitBytes, iss_map, iss_x, iss_y, bar0 + 8u * s);
             iss_y += kTileRows;
         }
         ++issued;
         --iss_left;
         if (++iss_t == iss_tiles) {
             iss_t = 0; iss_y = 0; iss_x += kChunkBytes;
-            if (iss_src) iss_src += iss_wrap;
+            if (ALL_PANELS || iss_src) iss_src += iss_wrap;
         }
         return true;
     };
-    if (tid == 0 && !iss_src) asm volatile("prefetch.tensormap [%0];" ::"l"(iss_map) : "memory");
+    if (!ALL_PANELS && tid == 0 && !iss_src) asm volatile("prefetch.tensormap [%0];" ::"l"(iss_map) : "memory");
 
     // Let the next kernel in the stream start its own prologue as SMs free up, then wait until
     // everything before this kernel has finished before touching activations or the workspace.
@@ -522,13 +550,11 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                 for (int k = 0; k < 4; ++k) xv[k] = __half2float(xh[x0 + 32 * k]);
                 // The activation loads are in flight: now top up this warp's weight tiles (issued the other
                 // way round the few activation bytes queue behind megabytes of weight traffic).
-                if (lane == 0)
-                    while (issued - consumed < kStages - 1 && issue_one()) {}
+                while (issued - consumed < kStages - 1 && issue_one()) {}
             } else {
                 // Output of an earlier link: keep the weight pipeline full, then wait (bounded) for exactly the
                 // words this lane needs.
-                if (lane == 0)
-                    while (issued - consumed < kStages - 1 && issue_one()) {}
+                while (issued - consumed < kStages - 1 && issue_one()) {}
                 const unsigned want = tag_base + (unsigned)L.src_tag + 1u;
                 unsigned long long wv[4];
 #pragma unroll
@@ -597,8 +623,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                 base[48] = (unsigned char)(d >> 24);
             }
         } else {
-            if (lane == 0)
-                while (issued - consumed < kStages - 1 && issue_one()) {}
+            while (issued - consumed < kStages - 1 && issue_one()) {}
             PHASE(0)
         }
         PHASE(4)
@@ -675,7 +700,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             for (int i = 0; i < seg; ++i) {
                 const uint32_t s = (uint32_t)consumed % kStages;
                 const uint32_t parity = ((uint32_t)consumed / kStages) & 1u;
-                uint32_t arrived = mbar_try_wait(bar0 + 8u * s, parity);
+                uint32_t arrived = mbar_test_wait(bar0 + 8u * s, parity);
                 if (!arrived) arrived = slow_wait(bar0 + 8u * s, parity);
                 // (arrived >> 8) is zero, but only the hardware knows: the tile loads depend on the wait
                 const uint32_t tile_addr = ring_warp + s * kUnitBytes + (arrived >> 8);
@@ -737,7 +762,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                 // the stage consumed one iteration ago is free: refill it
                 ++consumed;
                 __syncwarp();
-                if (lane == 0 && issued - consumed < kStages - 1) issue_one();
+                if (issued - consumed < kStages - 1) issue_one();
 
                 // quad: lanes q=0 (groups 0,1) and q=2 (groups 2,3) -> chunk partial in lane q=0
                 acc1 += __shfl_down_sync(0xffffffffu, acc1, 2);
@@ -882,8 +907,11 @@ int device_state(DeviceState **out) {
         int sms = 0;
         err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (err != cudaSuccess || sms <= 0) return cuda_fail(err, "tq1 chain: SM count");
-        err = cudaFuncSetAttribute(tq1_gemv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        err = cudaFuncSetAttribute(tq1_gemv_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)(kWindowEnd + kHighBytes));
+        if (err == cudaSuccess)
+            err = cudaFuncSetAttribute(tq1_gemv_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(kWindowEnd + kHighBytes));
         if (err != cudaSuccess) return cuda_fail(err, "tq1 chain: shared memory opt-in");
         st.sm_count = sms;
         st.attr_set = true;
@@ -1065,8 +1093,15 @@ int gemv_chain_describe(const tq1_chain_link *links, int n_links, int rank, int 
     return TQ1_OK;
 }
 
+// True when every link's weights are chunk-major panels (the kernel variant without the 2-D TMA path).
+bool all_panels(const ChainLinkDev *links, int n) {
+    for (int i = 0; i < n; ++i)
+        if (!(links[i].flags & kFlagPanels)) return false;
+    return n > 0;
+}
+
 int gemv_chain_launch(const ChainLinkDev *table_dev, const ChainLinkDev *inline_links, int n_dev_links,
-                      unsigned tag_advance, void *workspace, size_t region_slots, int n_regions,
+                      bool panels_only, unsigned tag_advance, void *workspace, size_t region_slots, int n_regions,
                       cudaStream_t stream) {
     DeviceState *st = nullptr;
     int rc = device_state(&st);
@@ -1098,7 +1133,8 @@ int gemv_chain_launch(const ChainLinkDev *table_dev, const ChainLinkDev *inline_
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
-    cudaError_t err = cudaLaunchKernelEx(&cfg, tq1_gemv_chain_kernel, params);
+    cudaError_t err = panels_only ? cudaLaunchKernelEx(&cfg, tq1_gemv_chain_kernel<true>, params)
+                                  : cudaLaunchKernelEx(&cfg, tq1_gemv_chain_kernel<false>, params);
     if (err != cudaSuccess) return cuda_fail(err, "tq1 chain: launch");
     return TQ1_OK;
 }
@@ -1130,7 +1166,7 @@ int launch_gemv_single(const uint8_t *blocks, const __half *x, void *y, bool y_f
     if (rc != TQ1_OK) return rc;
     for (size_t i = 0; i < dev.size(); ++i) {          // row ranges of a very tall matrix: one launch each
         dev[i].tag = 0;
-        rc = gemv_chain_launch(nullptr, &dev[i], 1, 1u, workspace, region_slots, 1, stream);
+        rc = gemv_chain_launch(nullptr, &dev[i], 1, all_panels(&dev[i], 1), 1u, workspace, region_slots, 1, stream);
         if (rc != TQ1_OK) return rc;
     }
     return TQ1_OK;
@@ -1305,7 +1341,8 @@ int tq1_chain_plan_create(const tq1_chain_link *links, int n_links, const tq1_ch
 
 int tq1_chain_plan_run(const tq1_chain_plan *plan, void *stream) {
     if (!plan) return fail(TQ1_ERR_INVALID, "tq1_chain_plan_run: null plan");
-    return gemv_chain_launch(plan->table_dev, nullptr, plan->n_dev_links, (unsigned)plan->n_links, plan->workspace,
+    return gemv_chain_launch(plan->table_dev, nullptr, plan->n_dev_links,
+                             all_panels(plan->host.data(), (int)plan->host.size()), (unsigned)plan->n_links, plan->workspace,
                              gemv_chain_region_slots(), 2, static_cast<cudaStream_t>(stream));
 }
 
@@ -1316,7 +1353,8 @@ int tq1_linear_chain_f16(const tq1_chain_link *links, int n_links, void *workspa
     std::vector<ChainLinkDev> dev;
     int rc = chain_describe_checked(links, n_links, nullptr, workspace, workspace_bytes, dev);
     if (rc != TQ1_OK) return rc;
-    return gemv_chain_launch(nullptr, dev.data(), (int)dev.size(), (unsigned)n_links, workspace,
+    return gemv_chain_launch(nullptr, dev.data(), (int)dev.size(), all_panels(dev.data(), (int)dev.size()),
+                             (unsigned)n_links, workspace,
                              gemv_chain_region_slots(), 2, static_cast<cudaStream_t>(stream));
 }
 
