@@ -46,6 +46,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <type_traits>
 #include <vector>
 
 #include "tq1_common.cuh"
@@ -275,10 +276,6 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
 
 // One lane-stream (half a block: 14 code-byte slots in four words, wa holding slots 0,1 in its
 // upper half) becomes 18 A registers: 14 table entries (weights of trits 0..3 of each slot) and
@@ -439,6 +436,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
 
     // ---- producer cursor: the next unit this warp requests, possibly of a later link ------------------
     int issued = 0, consumed = 0;               // units requested / finished by this warp since the launch began
+    uint32_t cstage = 0, cparity = 0;           // ring stage of the next unit to consume, and its barrier's phase
     int iss_link = 0, iss_left, iss_t, iss_tiles;
     int iss_x, iss_y;                           // canonical layout: TMA coordinates of the next unit
     const CUtensorMap *iss_map;
@@ -697,14 +695,15 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             }
             const int seg = min(left, tiles - t);       // units of this chunk
             left -= seg;
-            for (int i = 0; i < seg; ++i) {
-                const uint32_t s = (uint32_t)consumed % kStages;
-                const uint32_t parity = ((uint32_t)consumed / kStages) & 1u;
-                uint32_t arrived = mbar_test_wait(bar0 + 8u * s, parity);
-                if (!arrived) arrived = slow_wait(bar0 + 8u * s, parity);
+            // One unit. BAD: some group of the chunk holds NaN/Inf activations and takes the FP32 path (rare; kept out
+            // of the common loop so that it costs the common loop neither branches nor registers).
+            auto unit = [&](auto bad_tag) {
+                constexpr bool BAD = decltype(bad_tag)::value;
+                const uint32_t bar = bar0 + 8u * cstage;
+                uint32_t arrived = mbar_test_wait(bar, cparity);
+                if (!arrived) arrived = slow_wait(bar, cparity);
                 // (arrived >> 8) is zero, but only the hardware knows: the tile loads depend on the wait
-                const uint32_t tile_addr = ring_warp + s * kUnitBytes + (arrived >> 8);
-                const uint32_t a1 = tile_addr + lane_tile_off;
+                const uint32_t a1 = ring_warp + cstage * kUnitBytes + (arrived >> 8) + lane_tile_off;
                 float acc1 = 0.0f, acc2 = 0.0f;             // rows g and g+8, this lane's two groups
 #pragma unroll
                 for (int sub = 0; sub < 2; ++sub) {
@@ -720,22 +719,22 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                     uint32_t r1[kRegsPerSub], r2[kRegsPerSub];
                     decode_stream(w1a, w1b, w1c, w1d, lane_base, r1);
                     decode_stream(w2a, w2b, w2c, w2d, lane_base, r2);
-                    // two independent accumulator chains; register pairs 0..6 hold signed weights,
-                    // pairs 7,8 the raw (unsigned) code bytes
-                    int accA[4], accB[4];
-                    mma_bytes<true, true>(accA, r1[0], r2[0], r1[1], r2[1], breg[sub][0], breg[sub][1]);
-                    mma_bytes<true, true>(accB, r1[2], r2[2], r1[3], r2[3], breg[sub][2], breg[sub][3]);
-                    mma_bytes<true, false>(accA, r1[4], r2[4], r1[5], r2[5], breg[sub][4], breg[sub][5]);
-                    mma_bytes<true, false>(accB, r1[6], r2[6], r1[7], r2[7], breg[sub][6], breg[sub][7]);
-                    mma_bytes<true, false>(accA, r1[8], r2[8], r1[9], r2[9], breg[sub][8], breg[sub][9]);
-                    mma_bytes<true, false>(accB, r1[10], r2[10], r1[11], r2[11], breg[sub][10], breg[sub][11]);
-                    mma_bytes<true, false>(accA, r1[12], r2[12], r1[13], r2[13], breg[sub][12], breg[sub][13]);
-                    mma_bytes<false, false>(accB, r1[14], r2[14], r1[15], r2[15], breg[sub][14], breg[sub][15]);
-                    mma_bytes<false, false>(accA, r1[16], r2[16], r1[17], r2[17], breg[sub][16], breg[sub][17]);
+                    // One accumulator chain (splitting it in two or three measured the same and costs registers and
+                    // additions); register pairs 0..6 hold signed weights, pairs 7,8 the raw (unsigned) code bytes.
+                    int acc[4];
+                    mma_bytes<true, true>(acc, r1[0], r2[0], r1[1], r2[1], breg[sub][0], breg[sub][1]);
+                    mma_bytes<true, false>(acc, r1[2], r2[2], r1[3], r2[3], breg[sub][2], breg[sub][3]);
+                    mma_bytes<true, false>(acc, r1[4], r2[4], r1[5], r2[5], breg[sub][4], breg[sub][5]);
+                    mma_bytes<true, false>(acc, r1[6], r2[6], r1[7], r2[7], breg[sub][6], breg[sub][7]);
+                    mma_bytes<true, false>(acc, r1[8], r2[8], r1[9], r2[9], breg[sub][8], breg[sub][9]);
+                    mma_bytes<true, false>(acc, r1[10], r2[10], r1[11], r2[11], breg[sub][10], breg[sub][11]);
+                    mma_bytes<true, false>(acc, r1[12], r2[12], r1[13], r2[13], breg[sub][12], breg[sub][13]);
+                    mma_bytes<false, false>(acc, r1[14], r2[14], r1[15], r2[15], breg[sub][14], breg[sub][15]);
+                    mma_bytes<false, false>(acc, r1[16], r2[16], r1[17], r2[17], breg[sub][16], breg[sub][17]);
                     // columns: lane q=0 holds planes 0,1 of the first group, q=1 planes 2,3; q=2/3 the second group.
                     // Combine each lane's plane pair first, then one shuffle per row brings the upper pair over.
-                    const uint32_t pair1 = (uint32_t)(accA[0] + accB[0]) + ((uint32_t)(accA[1] + accB[1]) << 8);
-                    const uint32_t pair2 = (uint32_t)(accA[2] + accB[2]) + ((uint32_t)(accA[3] + accB[3]) << 8);
+                    const uint32_t pair1 = (uint32_t)acc[0] + ((uint32_t)acc[1] << 8);
+                    const uint32_t pair2 = (uint32_t)acc[2] + ((uint32_t)acc[3] << 8);
                     const uint32_t hi1 = __shfl_down_sync(0xffffffffu, pair1, 1);
                     const uint32_t hi2 = __shfl_down_sync(0xffffffffu, pair2, 1);
                     // Every lane does the arithmetic (no branch); only the even lanes of a quad hold meaningful
@@ -745,13 +744,13 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                     const int s2 = (int)((pair2 + (hi2 << 16) - (uint32_t)gsum[sub]) * 0x781948b1u);
                     float dot1 = (float)s1 * gpow[sub];
                     float dot2 = (float)s2 * gpow[sub];
-                    if (chunk_bad) {                        // warp-uniform and rare: NaN/Inf among the activations
+                    if (BAD) {
                         if (h == 0 && gbad[sub]) {
                             const int group = sub + 2 * cls;
-                            const unsigned char *tile = ring + (warp * kStages + s) * kUnitBytes;
+                            const unsigned char *tile = ring + (warp * kStages + cstage) * kUnitBytes;
                             const size_t x0 = ((size_t)c * kChunkGroups + group) * kGroup;
-                            dot1 = block_dot_fp32(tile + (g * kChunkGroups + group) * kBlockBytes, xh, xin, x0);
-                            dot2 = block_dot_fp32(tile + ((g + 8) * kChunkGroups + group) * kBlockBytes, xh, xin, x0);
+                            dot1 = block_dot_fp32(tile + (g * kChunkGroups + group) * kBlockBytes, L.x, L.xin, x0);
+                            dot2 = block_dot_fp32(tile + ((g + 8) * kChunkGroups + group) * kBlockBytes, L.x, L.xin, x0);
                         }
                     }
                     const float sc1 = __half2float(__ushort_as_half((unsigned short)(w1a & 0xffffu)));
@@ -761,6 +760,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                 }
                 // the stage consumed one iteration ago is free: refill it
                 ++consumed;
+                if (++cstage == kStages) { cstage = 0; cparity ^= 1u; }
                 __syncwarp();
                 if (issued - consumed < kStages - 1) issue_one();
 
@@ -773,6 +773,11 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                     slot_publish(mine + 8, acc2, tag);
                 }
                 mine += kTileRows;
+            };
+            if (!chunk_bad) {
+                for (int i = 0; i < seg; ++i) unit(std::false_type{});
+            } else {
+                for (int i = 0; i < seg; ++i) unit(std::true_type{});
             }
             t = 0;
             ++c;
