@@ -37,7 +37,7 @@ METRIC = "tq1_gemv_effective_hbm_gbps"
 UNIT = "GB/s"
 
 
-NCU_TRAFFIC_RATIO = (145.297 + 5.878) / 144.858     # DRAM read + write over algorithmic bytes, one 8-link chain launch
+NCU_TRAFFIC_RATIO = (145.336 + 4.787) / 144.858     # DRAM read + write over algorithmic bytes, one 8-link chain launch
 
 
 def parse_args():

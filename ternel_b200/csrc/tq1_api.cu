@@ -34,6 +34,8 @@ int tq1_linear_f16(const uint8_t *blocks, const void *x, void *y, int y_is_f32,
     if (M == 1 && gemv_chain_fits(blocks, N, K))
         return launch_gemv_single(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, N, K, false, workspace,
                                   kWsSlotRegionBytes, s);
+    if (gemv_looped_fits(blocks, M, N, K) && need >= kWsScratchOffset)
+        return launch_gemv_looped(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, false, workspace, s);
     if (gemm_tc_supported(blocks, static_cast<const __half *>(x), M, N, K))
         return launch_gemm_tc(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, workspace, s);
     return launch_gemv_rows(blocks, static_cast<const __half *>(x), y, y_is_f32 != 0, M, N, K, s);
@@ -58,6 +60,8 @@ int tq1_linear_swiglu_f16(const uint8_t *blocks, const void *x, void *y, int y_i
         return fail(TQ1_ERR_WORKSPACE, "tq1_linear_swiglu_f16: workspace of %zu bytes (256-byte aligned) required", need);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (gemv) return launch_gemv_single(blocks, xh, y, y_is_f32 != 0, rows, K, true, workspace, kWsSlotRegionBytes, s);
+    if (gemv_looped_fits(blocks, M, rows, K))
+        return launch_gemv_looped(blocks, xh, y, y_is_f32 != 0, M, rows, K, true, workspace, s);
     return launch_gemm_tc(blocks, xh, y, y_is_f32 != 0, M, rows, K, workspace, s, true);
 }
 
@@ -65,8 +69,8 @@ int tq1_linear_plan(int M, int N, int K, int aligned, int *kernel, int *token_ti
     if (!kernel || !token_tile || !ctas || !parts) return fail(TQ1_ERR_INVALID, "tq1_linear_plan: null pointer");
     if (M <= 0 || N <= 0 || K <= 0 || K % kGroup) return fail(TQ1_ERR_INVALID, "tq1_linear_plan: bad shape");
     *token_tile = *ctas = *parts = 0;
-    if (M == 1 && aligned && gemv_chain_shape_ok(N, K)) {
-        *kernel = TQ1_KERNEL_STREAM_GEMV;
+    if (M <= (gemv_loop_tokens() > 1 ? gemv_loop_tokens() : 1) && aligned && gemv_chain_shape_ok(N, K)) {
+        *kernel = TQ1_KERNEL_STREAM_GEMV;       // M > 1: one launch of M passes of the batch-1 kernel
     } else if (aligned && gemm_tc_shape_ok(M, N, K)) {
         *kernel = TQ1_KERNEL_TENSOR_CORE;
         gemm_tc_plan(M, N, K, token_tile, ctas, parts);
@@ -79,6 +83,13 @@ int tq1_linear_plan(int M, int N, int K, int aligned, int *kernel, int *token_ti
 // Sweep recording only (ternel_b200/dispatch.py binds it by name): forces the tensor-core kernel's token tile
 // for every later call of this process; 0 restores the rule. Process-global and not thread-safe, which is why
 // it is not part of the public header.
+// Sweep recording only: the largest batch that runs as passes of the batch-1 kernel (0: none).
+int tq1_debug_set_loop_tokens(int tokens) {
+    if (gemv_set_loop_tokens(tokens) != TQ1_OK)
+        return fail(TQ1_ERR_INVALID, "tq1_debug_set_loop_tokens: %d is not in 0..8", tokens);
+    return TQ1_OK;
+}
+
 int tq1_debug_force_token_tile(int token_tile) {
     if (gemm_tc_force_tile(token_tile) != TQ1_OK)
         return fail(TQ1_ERR_INVALID, "tq1_debug_force_token_tile: %d is not 0, 16, 32, 64, 128 or 256", token_tile);

@@ -85,6 +85,12 @@ bool gemv_chain_shape_ok(int N, int K);
 bool gemv_chain_supported(const uint8_t *blocks, int N, int K);
 bool gemv_chain_fits(const uint8_t *blocks, int N, int K);      // also checks the current device's SM count
 size_t gemv_chain_workspace_bytes(int N, int K);
+// M = 2 .. gemv_loop_tokens() activation rows as M links of one launch over the same weights
+bool gemv_looped_fits(const uint8_t *blocks, int M, int N, int K);
+int launch_gemv_looped(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int M, int N, int K, bool swiglu,
+                       void *workspace, cudaStream_t stream);
+int gemv_loop_tokens();
+int gemv_set_loop_tokens(int tokens);       // sweep recording only; process-global
 // slot_bytes: room for partial-sum slots behind the workspace's control words
 int launch_gemv_single(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int N, int K, bool swiglu,
                        void *workspace, size_t slot_bytes, cudaStream_t stream);

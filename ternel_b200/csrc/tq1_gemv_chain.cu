@@ -1178,6 +1178,49 @@ int launch_gemv_single(const uint8_t *blocks, const __half *x, void *y, bool y_f
 }
 
 
+// A few activation rows through the batch-1 kernel: one launch of M independent links over the same weights
+// (the second and later passes read them from L2). Faster than the batched kernel while M passes cost less
+// than its decode-to-tensor-memory pipeline; the crossover is recorded by the dispatch sweep.
+int launch_gemv_looped(const uint8_t *blocks, const __half *x, void *y, bool y_f32, int M, int N, int K, bool swiglu,
+                       void *workspace, cudaStream_t stream) {
+    int grid = 0;
+    int rc = gemv_chain_grid(&grid);
+    if (rc != TQ1_OK) return rc;
+    if (M < 1 || M > kInlineLinks) return fail(TQ1_ERR_INVALID, "tq1 chain: %d activation rows do not fit one launch", M);
+    tq1_chain_link links[kInlineLinks];
+    memset(links, 0, sizeof(links));
+    const size_t out_row = (size_t)(swiglu ? N / 2 : N) * (y_f32 ? sizeof(float) : sizeof(__half));
+    for (int m = 0; m < M; ++m) {
+        links[m].blocks = blocks; links[m].N = N; links[m].K = K;
+        links[m].x = x + (size_t)m * K;
+        links[m].y = static_cast<unsigned char *>(y) + (size_t)m * out_row;
+        links[m].y_is_f32 = y_f32; links[m].swiglu = swiglu; links[m].out_scale = 1.0f;
+    }
+    std::vector<ChainLinkDev> dev;
+    rc = gemv_chain_describe(links, M, 0, 1, nullptr, kRegionSlotsTwo, grid, dev);
+    if (rc != TQ1_OK) return rc;
+    if ((int)dev.size() != M) return fail(TQ1_ERR_INVALID, "tq1 chain: matrix too tall for the looped path");
+    return gemv_chain_launch(nullptr, dev.data(), M, all_panels(dev.data(), M), (unsigned)M, workspace,
+                             kRegionSlotsTwo, 2, stream);
+}
+
+// Largest M that tq1_linear_f16 sends through launch_gemv_looped (0 or 1: none).
+static int g_loop_tokens = 2;
+int gemv_loop_tokens() { return g_loop_tokens; }
+int gemv_set_loop_tokens(int tokens) {
+    if (tokens < 0 || tokens > kInlineLinks) return TQ1_ERR_INVALID;
+    g_loop_tokens = tokens;
+    return TQ1_OK;
+}
+// The looped path takes the shape when one link holds the whole matrix in one slot region of the two.
+bool gemv_looped_fits(const uint8_t *blocks, int M, int N, int K) {
+    if (M < 2 || M > g_loop_tokens || !gemv_chain_supported(blocks, N, K)) return false;
+    int grid = 0;
+    if (gemv_chain_grid(&grid) != TQ1_OK) return false;
+    if (rows_per_link(N, K, kRegionSlotsTwo) != N) return false;
+    return span_ok((N + kTileRows - 1) / kTileRows, K / kChunkCols, grid);
+}
+
 // Whether the chain kernel takes one product of this shape on the current device.
 bool gemv_chain_fits(const uint8_t *blocks, int N, int K) {
     if (!gemv_chain_supported(blocks, N, K)) return false;

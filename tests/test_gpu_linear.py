@@ -261,3 +261,22 @@ def test_device_byte_scan_counts_every_illegal_byte():
         validate_device_blocks(torch.from_numpy(bad.reshape(blocks.shape)).cuda())
     counts = torch.ops.ternel.tq1_validate(torch.from_numpy(bad.reshape(blocks.shape)).cuda()).cpu().tolist()
     assert counts == [n_full, n_tail]
+
+
+def test_two_rows_in_one_launch_equal_two_batch_1_calls():
+    """Batches the dispatch sends through the batch-1 kernel (one launch, one pass per activation row) give, row
+    by row, the bits of separate batch-1 calls."""
+    from ternel_b200.dispatch import looped_tokens
+    from ternel_b200.ops import tq1_matmul
+    tokens = looped_tokens()
+    if tokens < 2:
+        pytest.skip("the dispatch sends no batch through the batch-1 kernel")
+    blocks, rng = random_blocks(1040, 1024, seed=77)
+    x = rng.standard_normal((tokens, 1024)).astype(np.float16)
+    bd, xd = to_dev(blocks), to_dev(x)
+    both = tq1_matmul(bd, xd, out_dtype=torch.float32)
+    for m in range(tokens):
+        one = tq1_matmul(bd, xd[m:m + 1], out_dtype=torch.float32)
+        assert torch.equal(both[m:m + 1], one)
+    want = o.float64_matmul(blocks, x.astype(np.float32), rows=1040, columns=1024)
+    assert o.normalised_error(both.cpu().numpy(), want) < 1e-5
