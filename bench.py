@@ -79,9 +79,13 @@ def workload_config(args) -> dict:
         "launches_per_layer": "7 (q,k,v,o,gate,up,down)" if args.unfused else
                               "4 (q|k|v and gate|up stored row-concatenated: 7168x5120, 5120x5120, 34816x5120, 5120x17408)",
         "packed_weight_bytes": None,   # filled in
-        "parallelism": (f"row-sharded x{args.gpus}, shards exchanged by "
-                        + ("the chain kernel: tagged 64-bit words pushed to every rank over NVLink"
-                           if args.exchange == "chain" and args.batch == 1 else "NCCL all-gather")
+        "parallelism": ((f"x{args.gpus}: q|k|v and gate|up sharded by rows, o and down by columns (they read what their "
+                         "own rank produced; their FP32 partial sums and the row shards travel as tagged 64-bit words "
+                         "pushed to every rank over NVLink by the chain kernel)"
+                         if args.exchange == "chain" and args.batch == 1 and not args.unfused and not args.independent
+                         else f"row-sharded x{args.gpus}, shards exchanged by "
+                         + ("the chain kernel: tagged 64-bit words pushed to every rank over NVLink"
+                            if args.exchange == "chain" and args.batch == 1 else "NCCL all-gather"))
                         if args.gpus > 1 else "single GPU"),
         "step_launch": ("one persistent chain launch, every projection reads the previous one's output"
                         if args.exchange == "chain" and args.batch == 1 and not args.independent else
@@ -264,7 +268,11 @@ def verify_chain(stack, world: int, rank: int) -> dict:
     def gathered(i):
         y = outs[i]
         if world == 1:
-            return y
+            return y.to(torch.float16) if links[i].partial else y
+        if links[i].partial:        # a column shard: what the next link reads is the sum of the ranks' partial sums
+            total = y.clone()
+            dist.all_reduce(total)
+            return total.to(torch.float16)
         full = torch.empty((world, y.numel()), dtype=y.dtype, device=y.device)
         dist.all_gather_into_tensor(full, y.contiguous())
         return full.reshape(-1)

@@ -242,6 +242,7 @@ typedef struct tq1_chain_link {
     int swiglu;            /* rows are (gate, up) pairs: N/2 outputs */
     float out_scale;       /* multiplies every output; 0 is taken as 1 */
     int layout;            /* TQ1_LAYOUT_BLOCKS: `blocks` is canonical; TQ1_LAYOUT_PANELS: it is the panel form below */
+    int partial;           /* sharded chains only, see below: this rank holds a COLUMN range of the matrix, all N rows */
 } tq1_chain_link;
 
 /* Row-sharded chains: every rank runs the same list over its own rows of every matrix (rank r owns
@@ -250,7 +251,17 @@ typedef struct tq1_chain_link {
  * peer stores over NVLink, no multicast); readers poll their own memory. handoff[r] is rank r's
  * area (tq1_chain_handoff_bytes, zero-filled once, 256-byte aligned, mapped into this process).
  * Every rank must issue the same sequence of chain calls on its area. The reference has no
- * multi-device path (patches/prism-tq1-g128-distribution.patch:373). */
+ * multi-device path (patches/prism-tq1-g128-distribution.patch:373).
+ *
+ * A link may instead be sharded by COLUMNS (partial != 0): rank r holds columns [r * K, (r + 1) * K) of
+ * all N rows (`blocks`: that column range, canonical [N][K/128][28] or K/512 consecutive panels of the
+ * full matrix) and reads the matching K activations, for instance exactly the output rows this rank
+ * produced for a row-sharded link before it (source_offset = rank * n_out), so that hand-over needs no
+ * other GPU. Its output is the rank's partial sum (y, if given, receives the partial, after out_scale);
+ * the ranks' partial sums travel as FP32 words, and a link that reads a partial link receives their sum,
+ * added in rank order and rounded once to FP16 (source_offset then indexes the N summed outputs). Two
+ * row-sharded and two column-sharded projections per decoder layer halve the number of hand-overs that
+ * cross NVLink. swiglu and partial exclude each other. */
 typedef struct tq1_chain_peers {
     int rank, world;       /* world <= 8 */
     void *handoff[8];

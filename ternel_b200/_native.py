@@ -74,7 +74,7 @@ class ChainLink(ctypes.Structure):
     _fields_ = [
         ("blocks", c_void_p), ("N", c_int), ("K", c_int), ("x", c_void_p), ("source", c_int),
         ("source_offset", c_int), ("y", c_void_p), ("y_is_f32", c_int), ("swiglu", c_int),
-        ("out_scale", ctypes.c_float), ("layout", c_int),
+        ("out_scale", ctypes.c_float), ("layout", c_int), ("partial", c_int),
     ]
 
 

@@ -30,7 +30,9 @@ class Link:
     ``x``: FP16 ``[K]`` tensor complete before the launch, or ``None`` to read the output of link
     ``source`` (an earlier link) starting at element ``source_offset``. ``y``: optional output tensor
     (FP16 or FP32, ``N`` elements, ``N/2`` with ``swiglu``). With ``panel_rows > 0`` ``blocks`` holds the
-    chunk-major panel form of ``blocks_to_panels`` for a weight of that many rows.
+    chunk-major panel form of ``blocks_to_panels`` for a weight of that many rows. ``partial`` (sharded
+    chains): this rank holds a column range of the matrix, its output is a partial sum, and a link that
+    reads it receives the ranks' sum (see ``tq1_chain_peers`` in the header).
     """
 
     blocks: torch.Tensor
@@ -41,6 +43,7 @@ class Link:
     swiglu: bool = False
     out_scale: float = 1.0
     panel_rows: int = 0
+    partial: bool = False
 
     @property
     def rows(self) -> int:
@@ -88,6 +91,7 @@ def _pack_links(links: list[Link]):
             c.y, c.y_is_f32 = None, 0
         c.swiglu, c.out_scale = int(link.swiglu), float(link.out_scale)
         c.layout = 1 if link.panel_rows else 0
+        c.partial = int(link.partial)
     return array
 
 

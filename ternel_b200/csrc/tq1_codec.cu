@@ -93,7 +93,7 @@ using namespace tq1;
 
 extern "C" {
 
-int tq1_abi_version(void) { return 2; }
+int tq1_abi_version(void) { return 3; }
 
 #ifdef TQ1_BOUNDS_CHECK
 // {violations, code of the first, its index, its limit}; copies the record to host memory and clears it.

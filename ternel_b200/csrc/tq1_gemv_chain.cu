@@ -130,6 +130,9 @@ __device__ long long g_phase_acc[64 * kWarps * kPhases];
 constexpr unsigned kFlagOutF32 = 1u;
 constexpr unsigned kFlagSwiglu = 2u;
 constexpr unsigned kFlagPanels = 4u;           // weights in chunk-major panels: a unit is 1792 contiguous bytes
+constexpr unsigned kFlagPartialOut = 8u;       // the output is one rank's partial sum over its K shard: hand-off words carry FP32
+constexpr unsigned kFlagSrcF32 = 16u;          // the words this link reads carry FP32 partial sums (bits 8..11: how many to add)
+constexpr int kFlagSrcPartsShift = 8;
 
 // One link as the kernel sees it.
 struct alignas(128) ChainLinkDev {
@@ -140,7 +143,7 @@ struct alignas(128) ChainLinkDev {
     void *y;                                    // FP16/FP32 output, or null
     unsigned long long *xout[kMaxRanks];        // per rank: hand-off words of this link's output, at this rank's first
                                                 // output element (null: nobody reads this link inside the chain)
-    int N, tiles, chunks;
+    int N, src_stride, chunks;                  // src_stride: words from one rank's partial vector to the next rank's
     int units_q, units_r;                       // tiles * chunks = grid * units_q + units_r: CTA b takes units_q (+1 if b < units_r)
     int src_tag;                                // tag offset of the producing link
     int tag;                                    // tag offset of this link
@@ -329,15 +332,25 @@ __device__ __forceinline__ unsigned ctl_read(const unsigned *p) {
     return v;
 }
 
-// Activation `idx` of a link, whichever form it arrives in (the hand-off word has been waited for).
-__device__ __forceinline__ float link_x(const __half *x, const unsigned long long *xin, size_t idx) {
-    if (x) return __half2float(x[idx]);
-    return __half2float(__ushort_as_half((unsigned short)(word_read(xin + idx) & 0xffffu)));
+// Value carried by a hand-off word (the tag has been checked): an FP16 output, or one rank's FP32 partial sum.
+__device__ __forceinline__ float word_value(unsigned long long w, bool f32) {
+    return f32 ? __uint_as_float((uint32_t)w) : __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
 }
+// A sum of partial sums becomes the activation the next link reads by one rounding to FP16.
+__device__ __forceinline__ float round_to_half(float v) { return __half2float(__float2half_rn(v)); }
 
+// Activation `idx` of a link, whichever form it arrives in (the hand-off words have been waited for).
+__device__ float link_x(const ChainLinkDev &L, size_t idx) {
+    if (L.x) return __half2float(L.x[idx]);
+    const bool f32 = (L.flags & kFlagSrcF32) != 0;
+    const int parts = max(1, (int)((L.flags >> kFlagSrcPartsShift) & 15u));
+    float sum = 0.0f;
+    for (int r = 0; r < parts; ++r) sum += word_value(word_read(L.xin + (size_t)r * L.src_stride + idx), f32);
+    return f32 ? round_to_half(sum) : sum;
+}
 // FP32 fallback for one block (row-major canonical bytes in shared memory): multiplies every
 // weight so that NaN and Inf propagate exactly as in the reference.
-__device__ float block_dot_fp32(const uint8_t *blk, const __half *x, const unsigned long long *xin, size_t x0) {
+__device__ float block_dot_fp32(const uint8_t *blk, const ChainLinkDev &L, size_t x0) {
     float sum = 0.0f;
     for (int j = 0; j < kCodeBytes; ++j) {
         uint32_t v = blk[2 + j];
@@ -345,7 +358,7 @@ __device__ float block_dot_fp32(const uint8_t *blk, const __half *x, const unsig
         for (int i = 0; i < n; ++i) {
             const float w = (float)((int)(v % 3u) - 1);
             v /= 3u;
-            sum = fmaf(w, link_x(x, xin, x0 + 5 * j + i), sum);
+            sum = fmaf(w, link_x(L, x0 + 5 * j + i), sum);
         }
     }
     return sum;
@@ -444,8 +457,9 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
     size_t iss_wrap;                            // panels: extra bytes from a chunk's last tile to the next chunk's first
     auto cursor_load = [&]() {
         const ChainLinkDev &L = links[iss_link];
-        const WarpRange r = warp_range(L.tiles, L.units_q, L.units_r, warp);
-        iss_left = r.n_units; iss_t = r.t_first; iss_tiles = L.tiles;
+        const int l_tiles = (L.N + kTileRows - 1) / kTileRows;
+        const WarpRange r = warp_range(l_tiles, L.units_q, L.units_r, warp);
+        iss_left = r.n_units; iss_t = r.t_first; iss_tiles = l_tiles;
         iss_x = r.c_first * kChunkBytes; iss_y = r.t_first * kTileRows;
         iss_map = &L.wmap;
         iss_src = nullptr;
@@ -453,7 +467,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
             const PanelRef *ref = reinterpret_cast<const PanelRef *>(&L.wmap);
             const size_t stride = (size_t)ref->pad_rows * kChunkBytes;
             iss_src = ref->base + (size_t)r.c_first * stride + (size_t)r.t_first * kUnitBytes;
-            iss_wrap = stride - (size_t)L.tiles * kUnitBytes;
+            iss_wrap = stride - (size_t)l_tiles * kUnitBytes;
         }
     };
     cursor_load();
@@ -522,7 +536,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
 
     for (int p = 0; p < n_links; ++p) {
         const ChainLinkDev &L = links[p];
-        const int N = L.N, tiles = L.tiles, chunks = L.chunks;
+        const int N = L.N, tiles = (L.N + kTileRows - 1) / kTileRows, chunks = L.chunks;
         const __half *xh = L.x;
         const unsigned long long *xin = L.xin;
         const unsigned flags = L.flags;
@@ -554,19 +568,33 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                 // words this lane needs.
                 while (issued - consumed < kStages - 1 && issue_one()) {}
                 const unsigned want = tag_base + (unsigned)L.src_tag + 1u;
-                unsigned long long wv[4];
+                const bool src_f32 = (flags & kFlagSrcF32) != 0;
+                const int parts = max(1, (int)((flags >> kFlagSrcPartsShift) & 15u));
+                const size_t part_stride = (size_t)L.src_stride;
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    wv[k] = TQ1_IN_BOUNDS(x0 + 32 * k, (size_t)chunks * kChunkCols, 14u)
-                                ? word_read(xin + x0 + 32 * k) : ((unsigned long long)want << 32);
+                for (int k = 0; k < 4; ++k) xv[k] = 0.0f;
+                // one pass per rank that contributed a partial sum (a single pass for an ordinary source); the
+                // partial sums are added in rank order, so the result does not depend on arrival order
+                for (int r = 0; r < parts; ++r) {
+                    const unsigned long long *src = xin + (size_t)r * part_stride + x0;
+                    unsigned long long wv[4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    uint32_t spins = 0;
-                    while ((unsigned)(wv[k] >> 32) != want && !dead) {
-                        if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 4u); dead = true; break; }
-                        wv[k] = word_read(xin + x0 + 32 * k);
+                    for (int k = 0; k < 4; ++k)
+                        wv[k] = TQ1_IN_BOUNDS(x0 + 32 * k, (size_t)chunks * kChunkCols, 14u)
+                                    ? word_read(src + 32 * k) : ((unsigned long long)want << 32);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint32_t spins = 0;
+                        while ((unsigned)(wv[k] >> 32) != want && !dead) {
+                            if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 4u); dead = true; break; }
+                            wv[k] = word_read(src + 32 * k);
+                        }
+                        xv[k] += word_value(wv[k], src_f32);
                     }
-                    xv[k] = __half2float(__ushort_as_half((unsigned short)(wv[k] & 0xffffu)));
+                }
+                if (src_f32) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) xv[k] = round_to_half(xv[k]);
                 }
             }
             PHASE(0)
@@ -749,8 +777,8 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                             const int group = sub + 2 * cls;
                             const unsigned char *tile = ring + (warp * kStages + cstage) * kUnitBytes;
                             const size_t x0 = ((size_t)c * kChunkGroups + group) * kGroup;
-                            dot1 = block_dot_fp32(tile + (g * kChunkGroups + group) * kBlockBytes, L.x, L.xin, x0);
-                            dot2 = block_dot_fp32(tile + ((g + 8) * kChunkGroups + group) * kBlockBytes, L.x, L.xin, x0);
+                            dot1 = block_dot_fp32(tile + (g * kChunkGroups + group) * kBlockBytes, L, x0);
+                            dot2 = block_dot_fp32(tile + ((g + 8) * kChunkGroups + group) * kBlockBytes, L, x0);
                         }
                     }
                     const float sc1 = __half2float(__ushort_as_half((unsigned short)(w1a & 0xffffu)));
@@ -846,8 +874,11 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                             else static_cast<__half *>(y)[row] = hv;
                         }
                         // hand-off: the rounded FP16 value and this link's tag in one word, to every rank
+                        // (a partial sum over this rank's K shard travels as FP32: the reader adds the ranks' words)
+                        const uint32_t payload = (flags & kFlagPartialOut) ? __float_as_uint(total)
+                                                                           : (uint32_t)__half_as_ushort(hv);
                         for (int pr = 0; pr < world; ++pr)
-                            word_publish(L.xout[pr] + row, (uint32_t)__half_as_ushort(hv), tag);
+                            word_publish(L.xout[pr] + row, payload, tag);
                     }
                 }
                 t0 = 0;
@@ -1036,15 +1067,24 @@ int gemv_chain_describe(const tq1_chain_link *links, int n_links, int rank, int 
             return fail(TQ1_ERR_INVALID, "tq1 chain: link %d: %d rows cannot be (gate, up) pairs", i, l.N);
         if (world > 1 && (l.N % kTileRows))
             return fail(TQ1_ERR_INVALID, "tq1 chain: link %d: a shard of %d rows is not a multiple of %d", i, l.N, kTileRows);
+        if (l.partial && l.swiglu)
+            return fail(TQ1_ERR_INVALID, "tq1 chain: link %d: a partial sum cannot take the gated activation", i);
         const unsigned long long *xin = nullptr;
+        unsigned src_flags = 0u;
+        int src_stride = 0;
         if (!l.x) {
             const tq1_chain_link &s = links[l.source];
-            const long long have = (long long)link_out_local(s) * world;
+            // an ordinary source is the concatenation of the ranks' rows; a partial one is a sum of `world` vectors
+            const long long have = (long long)link_out_local(s) * (s.partial ? 1 : world);
             if (l.source_offset < 0 || (long long)l.source_offset + l.K > have)
                 return fail(TQ1_ERR_INVALID, "tq1 chain: link %d reads elements [%d, %d) of link %d, which has %lld",
                             i, l.source_offset, l.source_offset + l.K, l.source, have);
             if (!handoff || !handoff[rank]) return fail(TQ1_ERR_INVALID, "tq1 chain: no hand-off area");
             xin = handoff[rank] + offset[l.source] + l.source_offset;
+            if (s.partial) {
+                src_flags = kFlagSrcF32 | ((unsigned)world << kFlagSrcPartsShift);
+                src_stride = link_out_local(s);
+            }
         }
         const int step = rows_per_link(l.N, l.K, region_slots);
         if (step < l.N && l.swiglu && (step % 2))
@@ -1071,17 +1111,18 @@ int gemv_chain_describe(const tq1_chain_link *links, int n_links, int rank, int 
                 d.y = l.y_is_f32 ? static_cast<void *>(static_cast<float *>(l.y) + out0)
                                  : static_cast<void *>(static_cast<__half *>(l.y) + out0);
             d.N = rows;
-            d.tiles = (rows + kTileRows - 1) / kTileRows;
+            const int d_tiles = (rows + kTileRows - 1) / kTileRows;
+            d.src_stride = src_stride;
             d.chunks = l.K / kChunkCols;
-            d.units_q = d.tiles * d.chunks / grid;
-            d.units_r = d.tiles * d.chunks % grid;
-            if (!span_ok(d.tiles, d.chunks, grid))
+            d.units_q = d_tiles * d.chunks / grid;
+            d.units_r = d_tiles * d.chunks % grid;
+            if (!span_ok(d_tiles, d.chunks, grid))
                 return fail(TQ1_ERR_INVALID, "tq1 chain: link %d (%dx%d) spreads a CTA over more than %d K chunks",
                             i, l.N, l.K, kMaxChunksPerCta);
             d.src_tag = l.x ? 0 : l.source;
             d.tag = i;
             d.flags = (l.y_is_f32 ? kFlagOutF32 : 0u) | (l.swiglu ? kFlagSwiglu : 0u) |
-                      (l.layout == TQ1_LAYOUT_PANELS ? kFlagPanels : 0u);
+                      (l.layout == TQ1_LAYOUT_PANELS ? kFlagPanels : 0u) | (l.partial ? kFlagPartialOut : 0u) | src_flags;
             d.out_scale = l.out_scale == 0.0f ? 1.0f : l.out_scale;
             d.world = 0;
             if (consumed[i] || world > 1) {

@@ -110,7 +110,8 @@ class LayerStack:
     def __init__(self, *, layers: int, batch: int = 1, shape: LayerShape = LayerShape(),
                  vocab: int = 0, rank: int = 0, world: int = 1, device=None, seed: int = 0,
                  group=None, fused: bool = False, exchange: str = "chain", dependent: bool = True,
-                 panels: bool = True, weights_from: "LayerStack | None" = None) -> None:
+                 panels: bool = True, column_shards: bool = True,
+                 weights_from: "LayerStack | None" = None) -> None:
         self.layers, self.batch, self.shape = layers, batch, shape
         self.rank, self.world, self.group = rank, world, group
         self.device = torch.device(device if device is not None else "cuda")
@@ -129,14 +130,19 @@ class LayerStack:
         self.exchange = exchange
         self.dependent = dependent and exchange == "chain"
         self.use_panels = panels and exchange == "chain"
+        # Column shards (several ranks, dependent chain of the fused layer): o and down keep all their rows and a
+        # column range, so that o reads the q rows and down the SiLU*up rows this very rank produced; only the
+        # partial sums of o and down cross NVLink (two hand-overs per layer instead of four). q|k|v is then
+        # sharded like attention heads: every rank holds a slice of q, of k and of v.
+        self.column_shards = bool(column_shards and world > 1 and self.dependent and fused)
         # weights[l][j]: this rank's rows [rank*N/P, (rank+1)*N/P) of projection j in layer l
         if weights_from is not None:       # a second stack (another batch size) over the same resident weights
             if (weights_from.projections, weights_from.world, weights_from.layers) != (self.projections, world, layers):
                 raise ValueError("weights_from must have the same layers, projections and sharding")
             self.weights = weights_from.weights
         else:
-            self.weights = [[random_blocks_device(n // world, k, gen, self.device) for _, n, k in self.projections]
-                            for _ in range(layers)]
+            self.weights = [[random_blocks_device(*self.shard_shape(name, n, k, layer), gen, self.device)
+                             for name, n, k in self.projections] for layer in range(layers)]
         xg = torch.Generator(device=self.device)
         xg.manual_seed(seed + 7)   # same activations on every rank
         self.inputs = {k: torch.randn((batch, k), generator=xg, device=self.device).to(torch.float16)
@@ -163,6 +169,16 @@ class LayerStack:
             self.workspace = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=self.device)
             self.workspace_bytes = ws_bytes
 
+    def column_sharded(self, name: str, layer: int) -> bool:
+        """o and down of every layer, except the last down: the step's result stays an ordinary row shard."""
+        return self.column_shards and (name == "o" or (name == "down" and layer != self.layers - 1))
+
+    def shard_shape(self, name: str, n: int, k: int, layer: int) -> tuple[int, int]:
+        """(rows, columns) of this rank's part of a projection."""
+        if self.column_sharded(name, layer):
+            return n, k // self.world
+        return n // self.world, k
+
     # ------------------------------------------------------------------
     def chain_links(self, layers: "int | None" = None, panels: "bool | None" = None):
         """The step as chain links over this rank's weight shards (see the module docstring). With ``panels`` the
@@ -184,12 +200,15 @@ class LayerStack:
             base = len(links)
             for j, (name, n, k) in enumerate(self.projections):
                 swiglu = self.dependent and name == "gate_up"
-                n_out = (n // 2 if swiglu else n) // world
-                y = torch.zeros(n_out, dtype=torch.float16, device=self.device)
+                partial = self.column_sharded(name, layer)
+                rows, k = self.shard_shape(name, n, k, layer)
+                n_out = rows // 2 if swiglu else rows
+                # a column shard's output is a partial sum: kept in FP32 so that the ranks' parts can be compared
+                y = torch.zeros(n_out, dtype=torch.float32 if partial else torch.float16, device=self.device)
                 if panels:
-                    link = Link(blocks=self.panels[layer][j], panel_rows=n // world, y=y, swiglu=swiglu)
+                    link = Link(blocks=self.panels[layer][j], panel_rows=rows, y=y, swiglu=swiglu, partial=partial)
                 else:
-                    link = Link(blocks=blocks[j], y=y, swiglu=swiglu)
+                    link = Link(blocks=blocks[j], y=y, swiglu=swiglu, partial=partial)
                 if not self.dependent:
                     link.x = self.inputs[k][0]
                     link.out_scale = unit_gain(k)
@@ -202,14 +221,18 @@ class LayerStack:
                         link.source = base - 1                      # the previous layer's down projection
                 elif name == "o":
                     link.source, link.source_offset = base, 0       # the q part of q|k|v (or q itself)
-                    link.out_scale = unit_gain(k)
-                    assert q_rows == k
+                    if partial:                                     # this rank's own q rows: the head of its q|k|v slice
+                        link.source_offset = self.rank * (self.projections[0][1] // world)
+                    link.out_scale = unit_gain(k * (world if partial else 1))
+                    assert q_rows == k * (world if partial else 1)
                 elif name in ("gate_up", "gate", "up"):
                     link.source = base + (1 if self.fused else 3)   # the o projection
                     link.out_scale = swiglu_gain(1.0 / unit_gain(k)) if swiglu else unit_gain(k)
                 elif name == "down":
                     if self.fused:
                         link.source = base + 2                      # silu(gate) * up
+                        if partial:                                 # the rows of it this rank produced
+                            link.source_offset = self.rank * k
                     else:
                         link.x = self.inputs[k][0]                  # separate gate and up matrices cannot be fused here
                     link.out_scale = unit_gain(k)
@@ -243,13 +266,15 @@ class LayerStack:
             if link.swiglu:
                 gate, up = y[0::2], y[1::2]
                 y = gate / (1.0 + torch.exp(-gate)) * up
+            if link.partial and self.world > 1:             # a column shard: the output is the sum of the ranks' parts
+                dist.all_reduce(y, group=self.group)
             stats = torch.stack((y.double().pow(2).sum(), torch.tensor(float(y.numel()), dtype=torch.float64, device=y.device)))
-            if self.world > 1:
+            if self.world > 1 and not link.partial:
                 dist.all_reduce(stats, group=self.group)
             rms = math.sqrt(float(stats[0] / stats[1]))
             link.out_scale = 1.0 / max(rms, 1e-20)
             out = (y * link.out_scale).to(torch.float16)
-            if self.world > 1:
+            if self.world > 1 and not link.partial:
                 full = torch.empty((self.world, out.numel()), dtype=out.dtype, device=out.device)
                 dist.all_gather_into_tensor(full, out.contiguous(), group=self.group)
                 out = full.reshape(-1)
@@ -293,9 +318,10 @@ class LayerStack:
     def algorithmic_bytes_per_step(self) -> int:
         """Packed weights + FP16 activations in + FP16 outputs out, this rank, one step."""
         total = 0
-        for _, n, k in self.projections:
-            total += (n // self.world) * k // BLOCK_SIZE * BLOCK_BYTES + 2 * self.batch * (k + n // self.world)
-        total *= self.layers
+        for layer in range(self.layers):
+            for name, n, k in self.projections:
+                rows, columns = self.shard_shape(name, n, k, layer)
+                total += rows * columns // BLOCK_SIZE * BLOCK_BYTES + 2 * self.batch * (columns + rows)
         if self.vocab:
             total += self.batch * (self.shape.hidden // BLOCK_SIZE * BLOCK_BYTES + 2 * self.shape.hidden)
         return total

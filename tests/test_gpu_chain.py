@@ -305,3 +305,45 @@ def test_row_shards_are_pushed_into_every_ranks_hand_off_area():
             tags = (words >> 32).astype(np.uint32)
             assert np.array_equal(values, full)                  # every row, from both ranks, in both areas
             assert len(set(tags.tolist())) == 1 and tags[0] == step + 1      # one tag per call of the chain
+
+
+def test_column_shards_hand_over_partial_sums_that_the_reader_adds():
+    """Rank 0 of two, alone on the GPU: its o-like link holds all rows and the first half of the columns, so its
+    output is a partial sum that travels as an FP32 word. The other rank's partial sums are written into rank 0's
+    hand-off area by the test (same tag), so the next link finds both and must read their sum, rounded once to
+    FP16. A single-rank chain with a column-sharded link (one part) is checked the same way."""
+    from ternel_b200 import _native
+    from ternel_b200.chain import ChainPlan, Link, _pack_links
+    lib = _native.lib()
+    rows, columns, next_rows = 1024, 1024, 528
+    rng = np.random.default_rng(99)
+    w_part, _ = random_blocks(rows, columns // 2, seed=5)            # columns [0, 512) of the o-like matrix
+    w_next, _ = random_blocks(next_rows, rows, seed=6)
+    x_local = rng.standard_normal(columns // 2).astype(np.float16)
+    other = (rng.standard_normal(rows) * 0.3).astype(np.float32)      # what rank 1 would have pushed
+    part_want = o.float64_matmul(w_part, x_local[None, :].astype(np.float32), rows=rows, columns=columns // 2)[0] * 0.5
+    for world in (2, 1):
+        y_part = torch.zeros(rows, dtype=torch.float32, device="cuda")
+        y_next = torch.zeros(next_rows, dtype=torch.float32, device="cuda")
+        links = [Link(blocks=to_dev(w_part), x=to_dev(x_local), y=y_part, partial=True, out_scale=0.5),
+                 Link(blocks=to_dev(w_next), source=0, y=y_next)]
+        if world == 2:
+            nbytes = lib.tq1_chain_handoff_bytes(_pack_links(links), len(links), 2)
+            areas = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(2)]
+            words = (np.int64(1) << 32) | other.view(np.uint32).astype(np.int64)          # tag 1: link 0 of the first launch
+            areas[0][rows * 8: 2 * rows * 8].copy_(torch.from_numpy(words.view(np.uint8)).cuda())
+            plan = ChainPlan(links, peers=(0, 2, [a.data_ptr() for a in areas]))
+        else:
+            plan = ChainPlan(links)
+        plan.run()
+        torch.cuda.synchronize()
+        assert plan.status() == 0
+        got_part = y_part.cpu().numpy()
+        assert o.normalised_error(got_part[None, :], part_want[None, :].astype(np.float32)) < 1e-5
+        total = got_part + other if world == 2 else got_part
+        x_next = total.astype(np.float16)
+        want = o.float64_matmul(w_next, x_next[None, :].astype(np.float32), rows=next_rows, columns=rows)[0]
+        assert o.normalised_error(y_next.cpu().numpy()[None, :], want[None, :].astype(np.float32)) < 1e-5
+        if world == 2:      # rank 1's area received rank 0's partial sums as FP32 words
+            pushed = areas[1][: rows * 8].view(torch.int64).cpu().numpy()
+            assert np.array_equal((pushed & 0xffffffff).astype(np.uint32).view(np.float32), got_part)
