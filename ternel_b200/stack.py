@@ -134,7 +134,7 @@ class LayerStack:
         # column range, so that o reads the q rows and down the SiLU*up rows this very rank produced; only the
         # partial sums of o and down cross NVLink (two hand-overs per layer instead of four). q|k|v is then
         # sharded like attention heads: every rank holds a slice of q, of k and of v.
-        self.column_shards = bool(column_shards and world > 1 and self.dependent and fused)
+        self.column_shards = bool(column_shards and (world > 1 or column_shards == "always") and self.dependent and fused)
         # weights[l][j]: this rank's rows [rank*N/P, (rank+1)*N/P) of projection j in layer l
         if weights_from is not None:       # a second stack (another batch size) over the same resident weights
             if (weights_from.projections, weights_from.world, weights_from.layers) != (self.projections, world, layers):
@@ -266,18 +266,31 @@ class LayerStack:
             if link.swiglu:
                 gate, up = y[0::2], y[1::2]
                 y = gate / (1.0 + torch.exp(-gate)) * up
+            whole = y
             if link.partial and self.world > 1:             # a column shard: the output is the sum of the ranks' parts
-                dist.all_reduce(y, group=self.group)
-            stats = torch.stack((y.double().pow(2).sum(), torch.tensor(float(y.numel()), dtype=torch.float64, device=y.device)))
+                whole = y.clone()
+                dist.all_reduce(whole, group=self.group)
+            stats = torch.stack((whole.double().pow(2).sum(),
+                                 torch.tensor(float(whole.numel()), dtype=torch.float64, device=y.device)))
             if self.world > 1 and not link.partial:
                 dist.all_reduce(stats, group=self.group)
             rms = math.sqrt(float(stats[0] / stats[1]))
             link.out_scale = 1.0 / max(rms, 1e-20)
-            out = (y * link.out_scale).to(torch.float16)
-            if self.world > 1 and not link.partial:
-                full = torch.empty((self.world, out.numel()), dtype=out.dtype, device=out.device)
-                dist.all_gather_into_tensor(full, out.contiguous(), group=self.group)
-                out = full.reshape(-1)
+            if link.partial and self.world > 1:
+                # exactly the kernel's arithmetic (scale each part in FP32, add the parts in rank order, round once):
+                # SiLU*up makes the chain amplify any difference in scale between this pass and the real step
+                parts = torch.empty((self.world, y.numel()), dtype=torch.float32, device=y.device)
+                dist.all_gather_into_tensor(parts, (y * link.out_scale).contiguous(), group=self.group)
+                total = parts[0].clone()
+                for r in range(1, self.world):
+                    total += parts[r]
+                out = total.to(torch.float16)
+            else:
+                out = (y * link.out_scale).to(torch.float16)
+                if self.world > 1:
+                    full = torch.empty((self.world, out.numel()), dtype=out.dtype, device=out.device)
+                    dist.all_gather_into_tensor(full, out.contiguous(), group=self.group)
+                    out = full.reshape(-1)
             gathered[i] = out
             for j in [j for j in gathered if j < i - 8]:        # sources are never more than a layer back
                 del gathered[j]
