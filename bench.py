@@ -79,13 +79,9 @@ def workload_config(args) -> dict:
         "launches_per_layer": "7 (q,k,v,o,gate,up,down)" if args.unfused else
                               "4 (q|k|v and gate|up stored row-concatenated: 7168x5120, 5120x5120, 34816x5120, 5120x17408)",
         "packed_weight_bytes": None,   # filled in
-        "parallelism": ((f"x{args.gpus}: q|k|v and gate|up sharded by rows, o and down by columns (they read what their "
-                         "own rank produced; their FP32 partial sums and the row shards travel as tagged 64-bit words "
-                         "pushed to every rank over NVLink by the chain kernel)"
-                         if args.exchange == "chain" and args.batch == 1 and not args.unfused and not args.independent
-                         else f"row-sharded x{args.gpus}, shards exchanged by "
-                         + ("the chain kernel: tagged 64-bit words pushed to every rank over NVLink"
-                            if args.exchange == "chain" and args.batch == 1 else "NCCL all-gather"))
+        "parallelism": (f"row-sharded x{args.gpus}, shards exchanged by "
+                        + ("the chain kernel: tagged 64-bit words pushed to every rank over NVLink"
+                           if args.exchange == "chain" and args.batch == 1 else "NCCL all-gather")
                         if args.gpus > 1 else "single GPU"),
         "step_launch": ("one persistent chain launch, every projection reads the previous one's output"
                         if args.exchange == "chain" and args.batch == 1 and not args.independent else
@@ -431,6 +427,10 @@ def run_gpu_arm(args) -> None:
         per_gpu = alg_bytes_rank / (ms_per_step / 1e3) / 1e9
         cfg = workload_config(args)
         cfg["packed_weight_bytes"] = stack.packed_bytes_per_step * world
+        if world > 1 and chain and stack.column_sharded("o", 0):
+            cfg["parallelism"] = (f"x{world}: q|k|v and gate|up sharded by rows, o and down by columns (they read what their "
+                                  "own rank produced; their FP32 partial sums and the row shards travel as tagged 64-bit "
+                                  "words pushed to every rank over NVLink by the chain kernel)")
         cfg["cuda_graph"] = use_graph
         gemv_launches = 1 if chain else stack.links_per_step
         line = {
@@ -476,6 +476,7 @@ def run_gpu_arm(args) -> None:
                 "numpy_restatement": time_numpy_restatement(),
             }
         print(json.dumps(line))
+    graph = None        # a captured graph must not outlive the communicator whose kernels it may hold
     if world > 1:
         dist.destroy_process_group()
 

@@ -170,8 +170,12 @@ class LayerStack:
             self.workspace_bytes = ws_bytes
 
     def column_sharded(self, name: str, layer: int) -> bool:
-        """o and down of every layer, except the last down: the step's result stays an ordinary row shard."""
-        return self.column_shards and (name == "o" or (name == "down" and layer != self.layers - 1))
+        """o and down of every layer, except the last down (the step's result stays an ordinary row shard), where a
+        rank's column range is a whole number of 512-column chunks; otherwise the projection is sharded by rows."""
+        if not self.column_shards or not (name == "o" or (name == "down" and layer != self.layers - 1)):
+            return False
+        columns = {n_: k_ for n_, _, k_ in self.projections}[name]
+        return columns % (512 * self.world) == 0
 
     def shard_shape(self, name: str, n: int, k: int, layer: int) -> tuple[int, int]:
         """(rows, columns) of this rank's part of a projection."""
