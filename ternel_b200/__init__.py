@@ -28,4 +28,7 @@ def __getattr__(name):
                 "interleave_gate_up"):
         from . import ops
         return getattr(ops, name)
+    if name in ("ChainPlan", "Link", "linear_chain", "blocks_to_panels", "panels_to_blocks", "chain_workspace_bytes"):
+        from . import chain
+        return getattr(chain, name)
     raise AttributeError(name)

@@ -3,12 +3,16 @@
 Output rows of a packed linear are independent (each ``y[n]`` touches only row ``n``'s
 blocks), so rank ``r`` owns rows ``[r*N/P, (r+1)*N/P)`` of every projection: a contiguous byte
 range of the canonical weight. After a sharded projection every rank needs the whole FP16
-result again. Two exchanges are provided:
+result again. This module serves the batched kernels (two or more activation rows):
 
-* ``"p2p"`` (default): the producing kernel writes its rows straight into every rank's gathered
-  buffer over NVLink peer mappings and then raises a flag there (``tq1_linear_f16_sharded``);
-  the next kernel waits for the flags with a bounded spin. No collective kernel runs.
-* ``"nccl"``: ``all_gather_into_tensor`` after each projection (the baseline).
+* ``tq1_linear_f16_sharded``: a wait kernel (bounded spin on the tile flags of the activations
+  the call reads), the ordinary linear call on this rank's rows, and a push kernel that writes
+  the rows straight into every rank's gathered buffer over NVLink peer mappings and then raises
+  a per-tile flag there. No collective kernel runs.
+* the baseline is ``all_gather_into_tensor`` after each projection.
+
+Batch-1 decode shards inside the chain kernel instead (``ternel_b200.chain.ChainPlan`` with
+``peers``): outputs travel between projections and between GPUs as tagged 64-bit words.
 
 The reference is single-device (patches/prism-tq1-g128-distribution.patch:373), so this module
 has no counterpart there; the layout it shards is the reference's canonical block array.
