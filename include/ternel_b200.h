@@ -59,6 +59,12 @@ int tq1_pack_blocks(const uint8_t *scales, const uint8_t *trits, uint8_t *blocks
 int tq1_unpack_blocks(const uint8_t *blocks, uint8_t *scales, uint8_t *trits,
                       int64_t groups, int validate, int64_t *n_bad_full, int64_t *n_bad_tail);
 
+/* Replaces dequantize_row_tq1_g128 (patches/prism-tq1-g128-distribution.patch:423-440), the host-side
+ * "to_float" of the type: out[g * 128 + j] = (trit - 1) * scale_g as FP32, for `groups` consecutive
+ * blocks in host memory (a row, or any whole number of rows). Bytes are decoded as they are (validate at
+ * load). The device-side equivalent with row selection is tq1_embedding_f16. */
+int tq1_dequantize_blocks(const uint8_t *blocks, float *out, int64_t groups);
+
 /* The load-time scan of validate_packed_codes (src/ternel_mlx/packing.py:29-48)
  * and ggml_validate_row_data's TQ1 case (patches/prism-tq1-g128-distribution.patch:449-468),
  * over canonical blocks in host memory. */

@@ -27,6 +27,7 @@ SIGNATURES = {
     "tq1_pack_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, POINTER(c_int64)]),
     "tq1_unpack_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int,
                                   POINTER(c_int64), POINTER(c_int64)]),
+    "tq1_dequantize_blocks": (c_int, [c_void_p, c_void_p, c_int64]),
     "tq1_validate_blocks": (c_int, [c_void_p, c_int64, POINTER(c_int64), POINTER(c_int64)]),
     "tq1_tile_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
     "tq1_untile_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),

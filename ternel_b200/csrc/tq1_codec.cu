@@ -170,6 +170,25 @@ int tq1_unpack_blocks(const uint8_t *blocks, uint8_t *scales, uint8_t *trits,
     return TQ1_OK;
 }
 
+int tq1_dequantize_blocks(const uint8_t *blocks, float *out, int64_t groups) {
+    if (groups < 0 || (groups > 0 && (!blocks || !out)))
+        return fail(TQ1_ERR_INVALID, "tq1_dequantize_blocks: null pointer or negative group count");
+    float sign[256][5];                       // byte -> its five weights as -1, 0, +1
+    for (unsigned v = 0; v < 256; ++v) {
+        unsigned r = v;
+        for (int i = 0; i < 5; ++i) { sign[v][i] = (float)((int)(r % 3) - 1); r /= 3; }
+    }
+    for (int64_t g = 0; g < groups; ++g) {
+        const uint8_t *b = blocks + g * kBlockBytes;
+        const float d = __half2float(__ushort_as_half((unsigned short)(b[0] | (b[1] << 8))));
+        float *y = out + g * kGroup;
+        for (int j = 0; j < kFullBytes; ++j)
+            for (int i = 0; i < 5; ++i) y[5 * j + i] = sign[b[2 + j]][i] * d;
+        for (int i = 0; i < 3; ++i) y[125 + i] = sign[b[27]][i] * d;
+    }
+    return TQ1_OK;
+}
+
 int tq1_tile_blocks(const uint8_t *blocks, uint8_t *codes, uint16_t *scales,
                     int64_t rows, int64_t gpr, int64_t tile) {
     if (rows <= 0 || gpr <= 0 || tile <= 0 || !blocks || !codes || !scales)

@@ -89,6 +89,15 @@ def decode_tq1_blocks(blocks: npt.ArrayLike, *, validate: bool = True) -> tuple[
     return scales, codes
 
 
+def dequantize_blocks(blocks: npt.ArrayLike) -> np.ndarray:
+    """``(N, 28)`` blocks -> FP32 weights ``(N, 128)``, ``(trit - 1) * scale`` (the host-side ``to_float`` of the
+    type, ``dequantize_row_tq1_g128``, patches/prism-tq1-g128-distribution.patch:423-440)."""
+    packed = _as_blocks(blocks)
+    out = np.empty((packed.shape[0], BLOCK_SIZE), dtype=np.float32)
+    check(_native.lib().tq1_dequantize_blocks(_ptr(packed), _ptr(out), packed.shape[0]))
+    return out
+
+
 def validate_blocks(blocks: npt.ArrayLike) -> None:
     """Fail-closed scan of canonical blocks for bytes > 242 (full) / > 26 (tail)."""
     packed = _as_blocks(np.asarray(blocks).reshape(-1, BLOCK_BYTES) if np.asarray(blocks).ndim > 2 else blocks)

@@ -200,3 +200,20 @@ def test_c_abi_argument_checks_need_no_gpu():
     assert "multiple of the 128" in _native.last_error()
     assert lib.tq1_embedding_f16(p, p, p, 0, 0, 8, 128, None) == _native.TQ1_ERR_INVALID
     assert "indices are empty" in _native.last_error()
+
+
+def test_dequantize_blocks_is_the_decoded_trits_times_the_scale():
+    """The host-side to_float of the type against the oracle's decode: exact, including every byte value, negative
+    and subnormal scales and signed zeros."""
+    from ternel_b200.format import dequantize_blocks
+    from oracle import tq1_oracle as o
+    rng = np.random.default_rng(11)
+    groups = 300
+    trits = rng.integers(0, 3, size=(groups, 128), dtype=np.uint8)
+    scales = rng.normal(0.0, 0.05, size=groups).astype(np.float16)
+    scales[:4] = np.array([0.0, -0.0, 6e-8, -65504.0], dtype=np.float16)
+    blocks = o.encode_blocks(scales.view(np.uint8).reshape(-1, 2), trits)
+    got = dequantize_blocks(blocks)
+    want = (trits.astype(np.float32) - 1.0) * scales.astype(np.float32)[:, None]
+    assert got.dtype == np.float32 and got.shape == (groups, 128)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
