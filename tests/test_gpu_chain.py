@@ -347,3 +347,30 @@ def test_column_shards_hand_over_partial_sums_that_the_reader_adds():
         if world == 2:      # rank 1's area received rank 0's partial sums as FP32 words
             pushed = areas[1][: rows * 8].view(torch.int64).cpu().numpy()
             assert np.array_equal((pushed & 0xffffffff).astype(np.uint32).view(np.float32), got_part)
+
+
+def test_tags_close_to_wrapping_are_reported_and_results_stay_good():
+    """Word 2 of the workspace is the tag base. Once it passes 0xF0000000 a launch still computes correctly but
+    leaves status 7, which asks the caller to zero the workspace before the 32-bit tags wrap."""
+    from ternel_b200.chain import Link, chain_workspace_bytes, linear_chain
+    blocks, rng = random_blocks(528, 1024, seed=12)
+    x = rng.standard_normal(1024).astype(np.float16)
+    y0 = torch.zeros(528, dtype=torch.float32, device="cuda")
+    y1 = torch.zeros(528, dtype=torch.float32, device="cuda")
+    blocks2, _ = random_blocks(528, 512, seed=13)
+    links = [Link(blocks=to_dev(blocks), x=to_dev(x), y=y0), Link(blocks=to_dev(blocks2), source=0, y=y1)]
+    ws = torch.zeros(chain_workspace_bytes(links), dtype=torch.uint8, device="cuda")
+    words = ws[:16].view(torch.int32)
+    words[2] = -0x10000000 - 1                   # 0xEFFFFFFF: one launch of two links takes the base past 0xF0000000
+    linear_chain(links, ws)
+    torch.cuda.synchronize()
+    assert int(words[0].item()) == 7
+    want0 = o.float64_matmul(blocks, x[None, :].astype(np.float32), rows=528, columns=1024)[0]
+    assert o.normalised_error(y0.cpu().numpy()[None, :], want0[None, :].astype(np.float32)) < 1e-5
+    x1 = y0.cpu().numpy().astype(np.float16)[:512]
+    want1 = o.float64_matmul(blocks2, x1[None, :].astype(np.float32), rows=528, columns=512)[0]
+    assert o.normalised_error(y1.cpu().numpy()[None, :], want1[None, :].astype(np.float32)) < 1e-5
+    ws.zero_()                                   # what the caller does on status 7
+    linear_chain(links, ws)
+    torch.cuda.synchronize()
+    assert int(words[0].item()) == 0
