@@ -176,7 +176,11 @@ int tq1_shard_advance_epoch(uint32_t *epoch_base, uint32_t delta, void *stream);
 
 /* blocks: this rank's rows [N_local][K/128][28] (N_local a multiple of 16); x: the whole FP16
  * activations [M][K] in local memory. Waits are bounded: if a flag never arrives the status word
- * at the start of the workspace becomes 4 and the call completes with whatever was there. */
+ * at the start of the workspace becomes 4 and the call completes with whatever was there.
+ * Reuse of a gathered buffer: the flags order a reader after its writers, nothing orders a later
+ * writer after an earlier reader. A gathered buffer (and its flags) may therefore be written again
+ * only after every rank has finished the call that reads it, for instance by alternating two buffers
+ * per output size, or by a buffer per projection as the chain's hand-off areas do. */
 int tq1_linear_f16_sharded(const uint8_t *blocks, const void *x, const tq1_shard *shard,
                            int M, int N_local, int K, void *workspace, size_t workspace_bytes, void *stream);
 

@@ -25,7 +25,7 @@ def __getattr__(name):
         from . import packed_model
         return getattr(packed_model, name)
     if name in ("tq1_matmul", "tq1_gemm", "tq1_get_rows", "validate_device_blocks", "tq1_swiglu",
-                "interleave_gate_up"):
+                "interleave_gate_up", "check_status"):
         from . import ops
         return getattr(ops, name)
     if name in ("ChainPlan", "Link", "linear_chain", "blocks_to_panels", "panels_to_blocks", "chain_workspace_bytes"):

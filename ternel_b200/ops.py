@@ -48,6 +48,28 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
     return buf
 
 
+def check_status(device=None) -> None:
+    """Read the status word of the shared per-device workspace (synchronises the device).
+
+    Zero: every bounded wait inside the kernels was met. 7: results are good but the sequence tags are about
+    to wrap, so the workspace is zeroed here. Anything else raises: a wait ran out (the results of the calls
+    since the last check are not to be trusted) and the workspace is zeroed so that later calls start clean.
+    """
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _workspaces.get(index)
+    if buf is None:
+        return
+    torch.cuda.synchronize(device)
+    status = int(buf[:4].view(torch.int32)[0].item())
+    if status == 0:
+        return
+    buf.zero_()
+    if status != 7:
+        raise RuntimeError(f"a bounded wait inside a packed ternary kernel ran out (status {status}); "
+                           "the workspace has been reset")
+
+
 def _check_blocks(blocks: torch.Tensor) -> tuple[int, int]:
     if blocks.dtype != torch.uint8:
         raise FormatError(f"canonical blocks must be uint8, got {blocks.dtype}")

@@ -280,3 +280,19 @@ def test_two_rows_in_one_launch_equal_two_batch_1_calls():
         assert torch.equal(both[m:m + 1], one)
     want = o.float64_matmul(blocks, x.astype(np.float32), rows=1040, columns=1024)
     assert o.normalised_error(both.cpu().numpy(), want) < 1e-5
+
+
+def test_check_status_reads_the_shared_workspace():
+    from ternel_b200 import ops
+    blocks, rng = random_blocks(64, 512, seed=5)
+    x = rng.standard_normal((1, 512)).astype(np.float16)
+    ops.tq1_matmul(to_dev(blocks), to_dev(x))
+    ops.check_status()                                   # nothing ran out
+    buf = ops._workspaces[torch.cuda.current_device()]
+    buf[:4].view(torch.int32)[0] = 5                     # what a slot wait that ran out would leave
+    with pytest.raises(RuntimeError, match="status 5"):
+        ops.check_status()
+    assert int(buf[:4].view(torch.int32)[0].item()) == 0
+    y = ops.tq1_matmul(to_dev(blocks), to_dev(x), out_dtype=torch.float32)      # and later calls are clean
+    want = o.float64_matmul(blocks, x.astype(np.float32), rows=64, columns=512)
+    assert o.normalised_error(y.cpu().numpy(), want) < 1e-5
