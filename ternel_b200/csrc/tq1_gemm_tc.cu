@@ -208,6 +208,7 @@ struct WorkSplit {
     // and only the remaining tiles, numbered from whole_tiles on, are cut into ranges (total_iters counts
     // their iterations). Whole tiles need neither a partial store nor the fix-up.
     int whole_rounds, whole_tiles;
+    int tiles_total;                            // output tiles of the call (a CTA's last whole tiles may lie beyond)
     __host__ __device__ __forceinline__ int first_iter(int cta) const {
         if (cta >= ctas) return total_iters;
         if (splits == 0) return cta * quot + (cta < rem ? cta : rem);
@@ -236,13 +237,14 @@ struct GemmParams {
 // copies of the few numbers it needs: a reference to the kernel parameter would force the whole
 // parameter block into local memory.
 struct SegmentWalk {
-    int groups, whole_rounds, whole_tiles, cta, round, it, end, pieces;
+    int groups, whole_rounds, whole_tiles, tiles_total, cta, round, it, end, pieces;
     __device__ __forceinline__ SegmentWalk(const WorkSplit work, int cta_)
-        : groups(work.groups), whole_rounds(work.whole_rounds), whole_tiles(work.whole_tiles), cta(cta_), round(0),
+        : groups(work.groups), whole_rounds(work.whole_rounds), whole_tiles(work.whole_tiles),
+          tiles_total(work.tiles_total), cta(cta_), round(0),
           it(work.first_iter(cta_)), end(work.first_iter(cta_ + 1)), pieces(0) {}
     // slot: which of the CTA's two partial-tile slots a partial segment is stored to
     __device__ __forceinline__ bool next(int &tile, int &kb0, int &len, int &slot) {
-        if (round < whole_rounds) {
+        if (round < whole_rounds && cta * whole_rounds + round < tiles_total) {
             tile = cta * whole_rounds + round++;
             kb0 = 0;
             len = groups;
@@ -735,6 +737,12 @@ int sm_count_cached() {
     return sm_count[dev];
 }
 
+// Time per K block of one CTA by token tile, fitted to the recorded sweep (also used by token_tile()).
+constexpr float kSharingCostUs = 18.0f;
+float block_time_us(int nt) {
+    return nt <= 16 ? 0.85f : nt == 32 ? 0.5f : nt == 64 ? 0.55f : 0.8f;
+}
+
 // How the (tile, K block) iterations of a shape are dealt out for a given token tile.
 WorkSplit split_work(int nt, int M, int N, int K) {
     const long long tiles = (long long)((N + kTileW - 1) / kTileW) * ((M + nt - 1) / nt);
@@ -743,20 +751,32 @@ WorkSplit split_work(int nt, int M, int N, int K) {
     w.groups = K / kGroup;
     w.total_iters = (int)(tiles * w.groups);
     w.whole_rounds = w.whole_tiles = 0;
-    if (tiles >= slots) {
+    w.tiles_total = (int)tiles;
+    // With more than half as many tiles as slots, cutting every tile in two would need a second wave and one
+    // part per tile leaves up to half of the SMs idle: those shapes are shared stream-K fashion as well.
+    if (tiles >= slots || (nt > 16 && 2 * tiles > slots)) {
         w.splits = 0;
         w.ctas = (int)slots;
         // whole tiles first; what is left over is shared. A share of fewer than eight K blocks per CTA
         // would cost more in partial stores than it balances, so then one round of whole tiles is shared too.
         long long rounds = tiles / slots;
         long long shared = tiles - rounds * slots;
-        if (shared > 0 && shared * w.groups < 8 * slots) {
+        if (rounds > 0 && shared > 0 && shared * w.groups < 8 * slots) {
             --rounds;
             shared += slots;
+        }
+        // Sharing the leftover tiles saves the idle part of one more round of whole tiles, (1 - shared/slots) of
+        // a tile's time, and costs the partial tiles' round trip through the workspace and the fix-up launch
+        // (about 18 us measured at 256-token tiles). Short tiles that nearly fill a round run as whole tiles.
+        if (rounds > 0 && shared > 0 && shared < slots &&
+            (float)(slots - shared) / (float)slots * (float)w.groups * block_time_us(nt) < kSharingCostUs) {
+            ++rounds;
+            shared = 0;
         }
         w.whole_rounds = (int)rounds;
         w.whole_tiles = (int)(rounds * slots);
         w.total_iters = (int)(shared * w.groups);
+        if (shared == 0) w.ctas = (int)(tiles < rounds * slots ? (tiles + rounds - 1) / rounds : slots);
     } else {
         int splits = (int)(slots / tiles);
         const int max_splits = w.groups / 8 > 0 ? w.groups / 8 : 1;
