@@ -641,7 +641,12 @@ __global__ void tq1_permute_x_small_kernel(const __half *__restrict__ x, __half 
 // ascending K order (CTA order), so the result does not depend on timing. blockIdx.x + 1 names a boundary
 // between two CTAs' ranges; the block of the first boundary inside a tile handles that tile (eight token
 // columns per block in blockIdx.y, one thread per weight row). Tiles computed by one CTA were stored directly.
-constexpr int kFixCols = 4;
+// kFixCols token columns per thread: many small blocks where the tiles to complete are few (the call is
+// latency-bound there), sixteen columns for prefill shapes (fewer waves of blocks, more loads in flight).
+#ifndef TQ1_FIX_COLS_SMALL
+#define TQ1_FIX_COLS_SMALL 4
+#endif
+template <int kFixCols>
 __global__ void __launch_bounds__(kTileW)
 tq1_streamk_fixup_kernel(const float *__restrict__ partials, void *__restrict__ y, int y_f32,
                          int M, int N, int tiles_m, const WorkSplit work, int nt, int swiglu) {
@@ -957,9 +962,15 @@ int launch_gemm_tc(const uint8_t *blocks, const __half *x, void *y, bool y_f32, 
                                                   (work.rem != 0 || work.quot % work.groups != 0));
     if (ctas > 1 && shared_tiles) {
         const unsigned fix_blocks = work.splits > 0 ? (unsigned)(ctas / work.splits) : (unsigned)(ctas - 1);
-        const unsigned col_blocks = (unsigned)(((M < nt ? M : nt) + kFixCols - 1) / kFixCols);
-        tq1_streamk_fixup_kernel<<<dim3(fix_blocks, col_blocks), kTileW, 0, stream>>>(
-            partials, y, prm.y_f32, M, N, prm.tiles_m, work, nt, prm.swiglu);
+        const int cols = M < nt ? M : nt;
+        // sixteen columns per thread only where four would mean several waves of blocks
+        if ((long long)fix_blocks * ((cols + TQ1_FIX_COLS_SMALL - 1) / TQ1_FIX_COLS_SMALL) < 148 * 16)
+            tq1_streamk_fixup_kernel<TQ1_FIX_COLS_SMALL>
+                <<<dim3(fix_blocks, (unsigned)((cols + TQ1_FIX_COLS_SMALL - 1) / TQ1_FIX_COLS_SMALL)), kTileW, 0, stream>>>(
+                    partials, y, prm.y_f32, M, N, prm.tiles_m, work, nt, prm.swiglu);
+        else
+            tq1_streamk_fixup_kernel<16><<<dim3(fix_blocks, (unsigned)((cols + 15) / 16)), kTileW, 0, stream>>>(
+                partials, y, prm.y_f32, M, N, prm.tiles_m, work, nt, prm.swiglu);
         err = cudaGetLastError();
         if (err != cudaSuccess) return cuda_fail(err, "tq1_linear_f16: stream-K fix-up launch");
     }
