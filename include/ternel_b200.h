@@ -260,8 +260,10 @@ typedef struct tq1_chain_link {
  * as a 64-bit word {FP16 bits, sequence tag}, straight into the hand-off area of EVERY rank (plain
  * peer stores over NVLink, no multicast); readers poll their own memory. handoff[r] is rank r's
  * area (tq1_chain_handoff_bytes, zero-filled once, 256-byte aligned, mapped into this process).
- * Every rank must issue the same sequence of chain calls on its area. The reference has no
- * multi-device path (patches/prism-tq1-g128-distribution.patch:373).
+ * Every rank must issue the same sequence of chain calls on its area, and start a call within the
+ * bounded wait of its peers (2^21 polls, some tenths of a second): a link that waits longer for another
+ * rank's words gives up with status 4. The reference has no multi-device path
+ * (patches/prism-tq1-g128-distribution.patch:373).
  *
  * A link may instead be sharded by COLUMNS (partial != 0): rank r holds columns [r * K, (r + 1) * K) of
  * all N rows (`blocks`: that column range, canonical [N][K/128][28] or K/512 consecutive panels of the
