@@ -582,15 +582,22 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                     for (int k = 0; k < 4; ++k)
                         wv[k] = TQ1_IN_BOUNDS(x0 + 32 * k, (size_t)chunks * kChunkCols, 14u)
                                     ? word_read(src + 32 * k) : ((unsigned long long)want << 32);
+                    // words that have not arrived are read again together: one round trip after the last of
+                    // them lands, however many were late
+                    for (uint32_t spins = 0; !dead; ++spins) {
+                        bool missing = false;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        uint32_t spins = 0;
-                        while ((unsigned)(wv[k] >> 32) != want && !dead) {
-                            if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 4u); dead = true; break; }
-                            wv[k] = word_read(src + 32 * k);
+                        for (int k = 0; k < 4; ++k) {
+                            if ((unsigned)(wv[k] >> 32) != want) {
+                                wv[k] = word_read(src + 32 * k);
+                                missing = true;
+                            }
                         }
-                        xv[k] += word_value(wv[k], src_f32);
+                        if (!missing) break;
+                        if (spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 4u); dead = true; }
                     }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) xv[k] += word_value(wv[k], src_f32);
                 }
                 if (src_f32) {
 #pragma unroll
@@ -844,17 +851,23 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                         for (int k = 0; k < 8; ++k)
                             v[k] = c0 + 2 * k < chunks ? slot_read(ps + (size_t)(c0 + 2 * k) * stride)
                                                        : ((unsigned long long)tag << 32);
+                        // partial sums that have not arrived are read again together (one round trip after the
+                        // last of them lands); absent chunks were given the tag above
+                        for (uint32_t spins = 0; !dead; ++spins) {
+                            bool missing = false;
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            if (c0 + 2 * k < chunks) {
-                                uint32_t spins = 0;
-                                while ((unsigned)(v[k] >> 32) != tag && !dead) {
-                                    if (++spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 5u); dead = true; break; }
+                            for (int k = 0; k < 8; ++k) {
+                                if ((unsigned)(v[k] >> 32) != tag) {
                                     v[k] = slot_read(ps + (size_t)(c0 + 2 * k) * stride);
+                                    missing = true;
                                 }
-                                total += __uint_as_float((uint32_t)v[k]);
                             }
+                            if (!missing) break;
+                            if (spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 5u); dead = true; }
                         }
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            if (c0 + 2 * k < chunks) total += __uint_as_float((uint32_t)v[k]);
                     }
                     total += __shfl_xor_sync(0xffffffffu, total, 16);
                     int row = tt * kTileRows + r;
