@@ -575,6 +575,29 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                 for (int k = 0; k < 4; ++k) xv[k] = 0.0f;
                 // one pass per rank that contributed a partial sum (a single pass for an ordinary source); the
                 // partial sums are added in rank order, so the result does not depend on arrival order
+                if (parts == 2) {
+                    // two ranks' partial sums: all eight words of the lane are in flight together
+                    const unsigned long long *src0 = xin + x0, *src1 = xin + part_stride + x0;
+                    unsigned long long wa[4], wb[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const bool in = TQ1_IN_BOUNDS(x0 + 32 * k, (size_t)chunks * kChunkCols, 14u);
+                        wa[k] = in ? word_read(src0 + 32 * k) : ((unsigned long long)want << 32);
+                        wb[k] = in ? word_read(src1 + 32 * k) : ((unsigned long long)want << 32);
+                    }
+                    for (uint32_t spins = 0; !dead; ++spins) {
+                        bool missing = false;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            if ((unsigned)(wa[k] >> 32) != want) { wa[k] = word_read(src0 + 32 * k); missing = true; }
+                            if ((unsigned)(wb[k] >> 32) != want) { wb[k] = word_read(src1 + 32 * k); missing = true; }
+                        }
+                        if (!missing) break;
+                        if (spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 4u); dead = true; }
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) xv[k] = (0.0f + word_value(wa[k], src_f32)) + word_value(wb[k], src_f32);
+                } else
                 for (int r = 0; r < parts; ++r) {
                     const unsigned long long *src = xin + (size_t)r * part_stride + x0;
                     unsigned long long wv[4];
@@ -845,30 +868,37 @@ __global__ void __launch_bounds__(kThreads, 1) tq1_gemv_chain_kernel(const __gri
                     // warp-uniform: this warp owns row tile tt
                     const unsigned long long *ps = slots + (size_t)tt * kTileRows + r;
                     float total = 0.0f;
-                    for (int c0 = hf; c0 < chunks; c0 += 16) {
-                        unsigned long long v[8];
+                    // BATCH slots per lane are in flight together; links with more than 16 chunks take the wide form
+                    // (one round trip for K up to 18432 columns), the others the short one (fewer instructions)
+                    auto gather = [&](auto batch_tag) {
+                        constexpr int BATCH = decltype(batch_tag)::value;
+                        for (int c0 = hf; c0 < chunks; c0 += 2 * BATCH) {
+                            unsigned long long v[BATCH];
 #pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            v[k] = c0 + 2 * k < chunks ? slot_read(ps + (size_t)(c0 + 2 * k) * stride)
-                                                       : ((unsigned long long)tag << 32);
-                        // partial sums that have not arrived are read again together (one round trip after the
-                        // last of them lands); absent chunks were given the tag above
-                        for (uint32_t spins = 0; !dead; ++spins) {
-                            bool missing = false;
+                            for (int k = 0; k < BATCH; ++k)
+                                v[k] = c0 + 2 * k < chunks ? slot_read(ps + (size_t)(c0 + 2 * k) * stride)
+                                                           : ((unsigned long long)tag << 32);
+                            // partial sums that have not arrived are read again together (one round trip after the
+                            // last of them lands); absent chunks were given the tag above
+                            for (uint32_t spins = 0; !dead; ++spins) {
+                                bool missing = false;
 #pragma unroll
-                            for (int k = 0; k < 8; ++k) {
-                                if ((unsigned)(v[k] >> 32) != tag) {
-                                    v[k] = slot_read(ps + (size_t)(c0 + 2 * k) * stride);
-                                    missing = true;
+                                for (int k = 0; k < BATCH; ++k) {
+                                    if ((unsigned)(v[k] >> 32) != tag) {
+                                        v[k] = slot_read(ps + (size_t)(c0 + 2 * k) * stride);
+                                        missing = true;
+                                    }
                                 }
+                                if (!missing) break;
+                                if (spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 5u); dead = true; }
                             }
-                            if (!missing) break;
-                            if (spins > kMaxWaitSpins) { atomicExch(ctl + kCtlStatus, 5u); dead = true; }
-                        }
 #pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            if (c0 + 2 * k < chunks) total += __uint_as_float((uint32_t)v[k]);
-                    }
+                            for (int k = 0; k < BATCH; ++k)
+                                if (c0 + 2 * k < chunks) total += __uint_as_float((uint32_t)v[k]);
+                        }
+                    };
+                    if (chunks > 16) gather(std::integral_constant<int, 18>{});
+                    else gather(std::integral_constant<int, 8>{});
                     total += __shfl_xor_sync(0xffffffffu, total, 16);
                     int row = tt * kTileRows + r;
                     bool writer = hf == 0 && row < N;
