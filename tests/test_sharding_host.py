@@ -96,3 +96,26 @@ def test_two_gloo_ranks_shard_then_gather_equals_the_whole():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert results == {0: True, 1: True}
+
+
+def test_column_shards_only_where_a_rank_gets_whole_chunks():
+    """Which projections of the decode stack are sharded by columns (pure shape logic, no GPU): o and down, except
+    the last down, and only where K / world is a whole number of 512-column chunks; the shard shapes follow."""
+    from ternel_b200.stack import LayerShape, LayerStack
+
+    class Shapes(LayerStack):
+        def __init__(self, world, layers=3):
+            self.world, self.layers, self.column_shards = world, layers, world > 1
+            self.projections = LayerShape().projections(True)
+
+    one, two, four = Shapes(1), Shapes(2), Shapes(4)
+    assert not any(one.column_sharded(name, 0) for name, _, _ in one.projections)
+    assert [two.column_sharded(name, 0) for name, _, _ in two.projections] == [False, True, False, True]
+    assert not two.column_sharded("down", 2)                      # the step's result stays a row shard
+    assert two.shard_shape("o", 5120, 5120, 0) == (5120, 2560)
+    assert two.shard_shape("down", 5120, 17408, 0) == (5120, 8704)
+    assert two.shard_shape("down", 5120, 17408, 2) == (2560, 17408)
+    assert two.shard_shape("qkv", 7168, 5120, 0) == (3584, 5120)
+    # 5120 / 4 = 1280 and 17408 / 4 = 4352 are not multiples of 512: rows
+    assert not any(four.column_sharded(name, 0) for name, _, _ in four.projections)
+    assert four.shard_shape("o", 5120, 5120, 0) == (1280, 5120)
